@@ -169,3 +169,24 @@ class KuzipelConfig(ModelConfig):
             return list(range(n))
         a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
         return list(range(a)) + list(range(a, b)) * times + list(range(b, n))
+
+
+class PemidraConfig(ModelConfig):
+    """Pemidra (`"architecture": "Pemidra"`): `vocab`, `width`, `norm.eps`, `postln_alpha` and a list `layers`, each entry
+    with `type` ("retention", "general_delta" or "parallel"), the mixer's sizes and constants under `mixer` (a pair's under
+    `mixer.left` / `mixer.right`), and `mlp` (`{"kind": "dense", "ff": n}` or null)."""
+
+    KNOWN_KEYS = ("architecture", "vocab", "width", "norm", "postln_alpha", "layers", "torch_dtype", "dtype", "eos_token_id",
+                  "bos_token_id", "max_positions")
+
+    @property
+    def vocab_size(self) -> int:
+        return int(self.raw["vocab"])
+
+    @property
+    def hidden_size(self) -> int:
+        return int(self.raw["width"])
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.raw["layers"])

@@ -56,7 +56,7 @@ __global__ void paged_attention_generic_kernel(
     __syncthreads();
 
     const int* bt = block_table + (int64_t)seq * bt_stride;
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = imp_first_key(pos, window);
     const float* bias_h = bias ? bias + (int64_t)h * n_dist : nullptr;
     float m = -INFINITY, l = 0.f;
     float acc[ATT_ACC];            // dims tid + a * ATT_BLOCK
@@ -138,7 +138,7 @@ static int launch_generic(
                   "imp_paged_attention_generic: null pointer");
     IMP_CHECK_ARG(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "imp_paged_attention_generic: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
     IMP_CHECK_ARG(Dh > 0 && Dh <= ATT_MAX_DH, "imp_paged_attention_generic: head_dim %d outside (0, %d]", Dh, ATT_MAX_DH);
-    IMP_CHECK_ARG(page_size > 0 && num_pages > 0 && window >= 0, "imp_paged_attention_generic: bad cache geometry");
+    IMP_CHECK_ARG(page_size > 0 && num_pages > 0, "imp_paged_attention_generic: bad cache geometry");
     IMP_CHECK_ARG(Hq <= 65535, "imp_paged_attention_generic: more than 65535 query heads");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, Hq);

@@ -148,6 +148,15 @@ __device__ __forceinline__ void imp_report(int* status, int code) {
     if (status) atomicCAS(status, 0, code);
 }
 
+// The first key position a query at `pos` may see.  window == 0: every earlier key; window == W > 0: the last W
+// positions (pos - W + 1 and later); window == -C < 0: the keys of the query's own chunk, chunks of C positions
+// counted from position 0 of the sequence (floor(pos / C) * C and later).  Never decreasing in `pos`.
+__host__ __device__ __forceinline__ int imp_first_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -617,6 +617,230 @@ ModelPlan kuzipel_plan(const KuzipelConfig& cfg) {
     return plan;
 }
 
+// ------------------------------------------------------------------------------------ Pemidra
+PemidraConfig PemidraConfig::from_json(const Json& d, const std::string& where) {
+    PemidraConfig c;
+    c.architecture = d.get_string("architecture", "Pemidra");
+    c.vocab_size = positive("vocab", require_int(d, "vocab", where), where);
+    c.hidden_size = positive("width", require_int(d, "width", where), where);
+    c.max_position_embeddings = positive("max_positions", d.get_int("max_positions", 1 << 20), where);
+    c.torch_dtype = d.get_string("torch_dtype", d.get_string("dtype", "bfloat16"));
+    if (c.torch_dtype != "bfloat16" && c.torch_dtype != "float32")
+        bad(where + ": torch_dtype '" + c.torch_dtype + "' is not supported (bfloat16 or float32)");
+    if (const Json* eos = d.find("eos_token_id")) {
+        if (eos->is_array()) {
+            for (const auto& e : eos->items())
+                if (e.is_int()) c.eos_token_ids.push_back((int)e.as_int());
+        } else if (eos->is_int()) {
+            c.eos_token_ids.push_back((int)eos->as_int());
+        }
+    }
+    c.bos_token_id = d.get_int("bos_token_id", -1);
+    c.raw = d;
+    c.norm_eps = require_float(require_object(d, "norm", where), "eps", where + ": norm");
+    if (!(c.norm_eps > 0)) bad(where + ": norm.eps must be positive");
+    c.postln_alpha = require_float(d, "postln_alpha", where);
+    const Json& layers = require(d, "layers", where);
+    if (!layers.is_array() || layers.size() == 0) bad(where + ": 'layers' must be a non-empty list");
+    int i = 0;
+    for (const Json& lj : layers.items()) {
+        const std::string lw = where + ": layers[" + std::to_string(i++) + "]";
+        if (!lj.is_object()) bad(lw + " must be an object");
+        Layer l;
+        l.type = lj.get_string("type", "");
+        const Json& m = require_object(lj, "mixer", lw);
+        const std::string mw = lw + ".mixer";
+        if (l.type == "retention") {
+            l.heads = positive("heads", require_int(m, "heads", mw), mw);
+            l.dim = positive("dim", require_int(m, "dim", mw), mw);
+            l.vdim = positive("vdim", m.get_int("vdim", l.dim), mw);
+            const Json& dec = require(m, "decay", mw);
+            if (!dec.is_array() || (int64_t)dec.size() != l.heads) bad(mw + ": 'decay' must list a number per head (" + std::to_string(l.heads) + ")");
+            for (const Json& e : dec.items()) {
+                if (!e.is_number()) bad(mw + ": 'decay' must list numbers");
+                l.decay.push_back(e.as_double());
+            }
+        } else if (l.type == "general_delta") {
+            l.heads = positive("heads", require_int(m, "heads", mw), mw);
+            l.dim = positive("dim", require_int(m, "dim", mw), mw);
+            l.vdim = l.dim;
+            l.decay_rank = m.get_int("decay_rank", 0);
+        } else if (l.type == "parallel") {
+            const Json& a = require_object(m, "left", mw);
+            const Json& b = require_object(m, "right", mw);
+            const std::string aw = mw + ".left", bw = mw + ".right";
+            l.left.heads = positive("heads", require_int(a, "heads", aw), aw);
+            l.left.kv_heads = positive("kv_heads", a.get_int("kv_heads", l.left.heads), aw);
+            l.left.dim = positive("dim", require_int(a, "dim", aw), aw);
+            l.left.vdim = positive("vdim", a.get_int("vdim", l.left.dim), aw);
+            l.left.scale = require_float(a, "scale", aw);
+            if (!(l.left.scale > 0)) bad(aw + ": scale must be positive");
+            if (l.left.heads % l.left.kv_heads) bad(aw + ": heads " + std::to_string(l.left.heads) + " must be a multiple of kv_heads " + std::to_string(l.left.kv_heads));
+            if (const Json* mask = a.find("mask"))
+                if (mask->is_object()) l.left.chunk = positive("size", require_int(*mask, "size", aw + ".mask"), aw + ".mask");
+            if (const Json* rot = a.find("rot"))
+                if (rot->is_object()) {
+                    l.left.rot_dims = positive("dims", require_int(*rot, "dims", aw + ".rot"), aw + ".rot");
+                    l.left.rot_base = require_float(*rot, "base", aw + ".rot");
+                    if (l.left.rot_dims % 2 || l.left.rot_dims > l.left.dim) bad(aw + ".rot: dims " + std::to_string(l.left.rot_dims) + " must be even and within dim " + std::to_string(l.left.dim));
+                }
+            l.right.heads = positive("heads", require_int(b, "heads", bw), bw);
+            l.right.kv_heads = positive("kv_heads", b.get_int("kv_heads", l.right.heads), bw);
+            l.right.dim = positive("dim", require_int(b, "dim", bw), bw);
+            l.right.vdim = positive("vdim", b.get_int("vdim", l.right.dim), bw);
+            l.right.conv = positive("conv", require_int(b, "conv", bw), bw);
+            l.right.decay_rank = b.get_int("decay_rank", 0);
+            l.right.gate_rank = b.get_int("gate_rank", 0);
+            if (l.right.heads % l.right.kv_heads) bad(bw + ": heads " + std::to_string(l.right.heads) + " must be a multiple of kv_heads " + std::to_string(l.right.kv_heads));
+        } else {
+            bad(lw + ": unknown layer type '" + l.type + "' (known: retention, general_delta, parallel)");
+        }
+        if (const Json* f = lj.find("mlp")) {
+            if (f->is_object()) {
+                const std::string kind = f->get_string("kind", "");
+                if (kind != "dense") bad(lw + ".mlp: unknown kind '" + kind + "' (known: dense)");
+                l.ff = positive("ff", require_int(*f, "ff", lw + ".mlp"), lw + ".mlp");
+            } else if (!f->is_null()) {
+                bad(lw + ".mlp must be an object or null");
+            }
+        }
+        c.layers.push_back(l);
+    }
+    c.num_hidden_layers = (int64_t)c.layers.size();
+    return c;
+}
+
+Json PemidraConfig::to_json() const {
+    Json j = raw.is_object() ? raw : Json::object();
+    j["architecture"] = architecture;
+    j["vocab"] = vocab_size;
+    j["width"] = hidden_size;
+    j["torch_dtype"] = torch_dtype;
+    j.erase("dtype");
+    return j;
+}
+
+// Layer i's tensors are 'l<i>.norm1' (+ '.b'), 'l<i>.ls1', 'l<i>.mix.*', and with a feed-forward 'l<i>.norm2' (+ '.b'),
+// 'l<i>.ls2', 'l<i>.mlp.*'; a pair's mixers live under 'mix.left.' and 'mix.right.'.
+ModelPlan pemidra_plan(const PemidraConfig& cfg) {
+    const int64_t d = cfg.hidden_size;
+    ModelPlan plan;
+    plan.architecture = cfg.architecture;
+    plan.hidden_size = d;
+    plan.vocab_size = cfg.vocab_size;
+    plan.max_positions = cfg.max_position_embeddings;
+    auto norm = [&](const std::string& tensor) {
+        PartSpec n;
+        n.kind = "layernorm";
+        n.params["size"] = d;
+        n.params["eps"] = cfg.norm_eps;
+        n.params["bias"] = true;
+        n.tensors = {{"weight", tensor}, {"bias", tensor + ".b"}};
+        return n;
+    };
+    for (size_t i = 0; i < cfg.layers.size(); ++i) {
+        const PemidraConfig::Layer& l = cfg.layers[i];
+        const std::string p = "l" + std::to_string(i) + ".", a = p + "mix.";
+        LayerSpec layer;
+        layer.block = "postnorm";
+        layer.block_params["hidden_size"] = d;
+        layer.block_params["residual_mult"] = cfg.postln_alpha;
+        layer.block_params["has_ffn"] = l.ff > 0;
+        layer.block_params["pair"] = l.type == "parallel";
+        layer.block_params["pair_eps"] = cfg.norm_eps;
+        layer.block_tensors = {{"mixer_scale", p + "ls1"}};
+        layer.parts = {{"mixer_norm", norm(p + "norm1")}};
+        if (l.type == "retention") {
+            PartSpec m;
+            m.kind = "retention";
+            m.params["hidden_size"] = d;
+            m.params["num_heads"] = l.heads;
+            m.params["key_dim"] = l.dim;
+            m.params["value_dim"] = l.vdim;
+            m.params["norm_eps"] = cfg.norm_eps;
+            Json dec = Json::array();
+            for (double v : l.decay) dec.push(Json(v));
+            m.params["decay"] = dec;
+            m.tensors = {{"q_proj", a + "q"}, {"k_proj", a + "k"}, {"v_proj", a + "v"}, {"gate_proj", a + "g"}, {"o_proj", a + "o"}};
+            layer.parts.emplace_back("mixer", m);
+        } else if (l.type == "general_delta") {
+            PartSpec m;
+            m.kind = "general_delta";
+            m.params["hidden_size"] = d;
+            m.params["num_heads"] = l.heads;
+            m.params["head_dim"] = l.dim;
+            m.params["norm_eps"] = cfg.norm_eps;
+            m.params["decay_rank"] = l.decay_rank;
+            m.tensors = {{"r_proj", a + "r"}, {"k_proj", a + "k"}, {"v_proj", a + "v"}, {"gate_proj", a + "g"}, {"a_proj", a + "a"},
+                         {"a_bias", a + "a.b"}, {"decay_down", a + "w1"}, {"decay_up", a + "w2"}, {"decay_bias", a + "w0"},
+                         {"out_norm", a + "norm"}, {"o_proj", a + "o"}};
+            layer.parts.emplace_back("mixer", m);
+        } else {
+            const std::string la = a + "left.", rb = a + "right.";
+            PartSpec left;
+            left.kind = "gated_head_attention";
+            left.params["hidden_size"] = d;
+            left.params["num_heads"] = l.left.heads;
+            left.params["num_kv_heads"] = l.left.kv_heads;
+            left.params["head_dim"] = l.left.dim;
+            left.params["value_dim"] = l.left.vdim;
+            left.params["scale"] = l.left.scale;
+            left.params["norm_eps"] = cfg.norm_eps;
+            left.params["qk_norm"] = true;
+            left.params["value_norm"] = true;
+            left.params["rot_dims"] = l.left.rot_dims;
+            left.params["rot_base"] = l.left.rot_base;
+            left.params["head_temp"] = true;
+            left.params["chunk"] = l.left.chunk;
+            left.params["sink"] = true;
+            left.params["head_gate"] = true;
+            left.tensors = {{"q_proj", la + "q"}, {"k_proj", la + "k"}, {"v_proj", la + "v"}, {"q_norm", la + "q.norm"}, {"k_norm", la + "k.norm"},
+                            {"head_temp", la + "temp"}, {"gate_proj", la + "g"}, {"o_proj", la + "o"}};
+            PartSpec right;
+            right.kind = "channel_delta_rule";
+            right.params["hidden_size"] = d;
+            right.params["num_heads"] = l.right.heads;
+            right.params["num_kv_heads"] = l.right.kv_heads;
+            right.params["key_dim"] = l.right.dim;
+            right.params["value_dim"] = l.right.vdim;
+            right.params["conv_taps"] = l.right.conv;
+            right.params["norm_eps"] = cfg.norm_eps;
+            right.params["decay_rank"] = l.right.decay_rank;
+            right.params["gate_rank"] = l.right.gate_rank;
+            right.tensors = {{"q_proj", rb + "q"}, {"q_conv", rb + "q.conv"}, {"k_proj", rb + "k"}, {"k_conv", rb + "k.conv"}, {"v_proj", rb + "v"},
+                             {"v_conv", rb + "v.conv"}, {"beta_proj", rb + "b"}, {"a_log", rb + "A_log"}, {"out_norm", rb + "norm"},
+                             {"decay_down", rb + "a1"}, {"decay_up", rb + "a2"}, {"dt_bias", rb + "dt_bias"}, {"gate_down", rb + "g1"},
+                             {"gate_up", rb + "g2"}, {"o_proj", rb + "o"}};
+            layer.parts.emplace_back("left", left);
+            layer.parts.emplace_back("right", right);
+            layer.block_tensors.emplace_back("left_out", la + "out");
+            layer.block_tensors.emplace_back("right_out", rb + "out");
+        }
+        if (l.ff > 0) {
+            PartSpec ffn;
+            ffn.kind = "gated_mlp";
+            ffn.params["hidden_size"] = d;
+            ffn.params["intermediate_size"] = l.ff;
+            ffn.params["activation"] = "gelu_tanh";
+            ffn.tensors = {{"gate_proj", p + "mlp.gate"}, {"up_proj", p + "mlp.up"}, {"down_proj", p + "mlp.down"}};
+            layer.block_tensors.emplace_back("ffn_scale", p + "ls2");
+            layer.parts.emplace_back("ffn_norm", norm(p + "norm2"));
+            layer.parts.emplace_back("feed_forward", ffn);
+        }
+        plan.layers.push_back(layer);
+    }
+    plan.embedding.kind = "token_embedding";
+    plan.embedding.params["vocab_size"] = cfg.vocab_size;
+    plan.embedding.params["hidden_size"] = d;
+    plan.embedding.tensors = {{"weight", "embed"}};
+    plan.final_norm = norm("final.norm");
+    plan.head.kind = "linear_head";
+    plan.head.params["vocab_size"] = cfg.vocab_size;
+    plan.head.params["hidden_size"] = d;
+    plan.head.tensors = {{"weight", "head"}};
+    return plan;
+}
+
 // ------------------------------------------------------------------------------------ registry
 namespace {
 std::mutex g_arch_mutex;
@@ -648,6 +872,13 @@ void ensure_builtin_archs() {
         };
         z.plan = [](const Json& d) { return kuzipel_plan(KuzipelConfig::from_json(d, "config.json")); };
         archs()[z.name] = z;
+        Architecture pm;
+        pm.name = "Pemidra";
+        pm.parse_config = [](const Json& d, const std::string& where) -> std::shared_ptr<ModelConfig> {
+            return std::make_shared<PemidraConfig>(PemidraConfig::from_json(d, where));
+        };
+        pm.plan = [](const Json& d) { return pemidra_plan(PemidraConfig::from_json(d, "config.json")); };
+        archs()[pm.name] = pm;
     });
 }
 }  // namespace

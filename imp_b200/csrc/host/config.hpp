@@ -115,6 +115,39 @@ struct KuzipelConfig : ModelConfig {
 
 ModelPlan kuzipel_plan(const KuzipelConfig& cfg);
 
+// Pemidra ("architecture": "Pemidra"): a post-norm decoder, x <- LN(alpha x + s1 (.) mixer(x)) and, where the layer has
+// one, x <- LN(alpha x + s2 (.) ffn(x)), with layer norms that have a weight and a bias.  A layer's mixer is retention, the
+// generalised delta rule, or a pair side by side (softmax attention with normalised, partly rotated, chunk-masked and gated
+// heads beside the delta rule with a decay per key channel) whose outputs are each RMS-normalised and averaged.  The
+// feed-forward is gated with the tanh form of gelu.  config.json lists the layers one by one; the keys are this family's own.
+struct PemidraConfig : ModelConfig {
+    struct Left {
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, chunk = 0, rot_dims = 0;
+        double scale = 0, rot_base = 10000.0;
+    };
+    struct Right {
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, conv = 0, decay_rank = 0, gate_rank = 0;
+    };
+    struct Layer {
+        std::string type;                       // "retention" | "general_delta" | "parallel"
+        int64_t heads = 0, dim = 0, vdim = 0;   // retention, general_delta
+        std::vector<double> decay;              // retention: a number per head
+        int64_t decay_rank = 0;                 // general_delta: 0 = the checkpoint's tensor decides
+        Left left;
+        Right right;
+        int64_t ff = 0;                         // 0 = the layer has no feed-forward
+    };
+    std::vector<Layer> layers;
+    double norm_eps = 1e-6, postln_alpha = 1.0;
+
+    static PemidraConfig from_json(const Json& d, const std::string& where);
+    Json to_json() const override;
+};
+
+// The inner sizes of the low-rank products are no config keys: the checkpoint's tensors give them; optional `decay_rank`
+// and `gate_rank` keys of a mixer fix them (random weights need them).
+ModelPlan pemidra_plan(const PemidraConfig& cfg);
+
 // ------------------------------------------------------------------------------------ registry
 struct Architecture {
     std::string name;

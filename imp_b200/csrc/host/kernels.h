@@ -112,6 +112,35 @@ int imp_add_layernorm(float* h, const void* branch, const float* col_scale, cons
 int imp_scale_columns(void* x, int64_t stride, int n_rows, int n_cols, const float* s, int dtype, void* stream);
 int imp_concat_streams(void* out, const float* h, const void* branch, const float* col_scale, const float* x0, int n_rows,
                        int d, int act_dtype, void* stream);
+int imp_add_layernorm_ex(float* h, float h_mult, const void* branch, const float* col_scale, const void* w, const void* bias, void* out,
+                         const int* rows, int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream);
+// the general scan over a decaying matrix state and the kernels around it (delta_rule.cu)
+int imp_lsr_scan(int mode, const float* kw, const float* q, const float* w, const float* p, const float* z, const float* v,
+                 const float* scal, const float* head_decay, float* state, float* out, const int* q_start, const int* slots,
+                 int n_seqs, int D, int H, int Dv, void* stream);
+int imp_retention_prepare(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, float* q, float* kw, float* v,
+                          float* scal, int act_dtype, void* stream);
+int imp_gdelta_prepare(const void* proj, int64_t ld, const float* dlog, const float* w0, const float* a_bias, float decay_scale,
+                       float unit_eps, int n_tokens, int H, int D, float* q, float* kw, float* w, float* p, float* z, float* v,
+                       float* scal, int act_dtype, void* stream);
+int imp_gdrc_prepare(const void* proj, int64_t ld, const float* conv_w, int taps, const float* conv_state, const int* seq_of_token,
+                     const int* q_start, const int* slots, int n_tokens, int n_seqs, int G, int D, int H, int Dv, const float* dpre,
+                     const float* a_log, const float* dt_bias, float unit_eps, float* q, float* kw, float* w, float* v, float* scal,
+                     int act_dtype, int* status, void* stream);
+int imp_gdr_output_ex(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, int w_head_stride, int gate_act,
+                      float eps, int n_tokens, int H, int Dv, int act_dtype, void* stream);
+// attention with normalised, partly rotated, scaled and gated heads; blocks of two mixers (qkv_prepare.cu)
+int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
+                    const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, const float* head_mult,
+                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* q_out,
+                    int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype, int* status,
+                    void* stream);
+int imp_head_gate(void* y, int64_t y_ld, const void* g, int64_t g_ld, int n_tokens, int H, int Dv, int dtype, void* stream);
+int imp_rms_pair_mean(void* out, const void* a, const float* wa, float ca, const void* b, const float* wb, float cb, int n_rows, int d,
+                      float eps, int dtype, void* stream);
+int imp_gated_act(void* out, const void* gate_up, int n_tokens, int F, int block, int act, int dtype, void* stream);
+int imp_act_rows(void* out, const void* x, int64_t ld, int n_tokens, int n, int act, int dtype, void* stream);
+int imp_gather_head_cols(void* dst, const void* src, int n_tokens, int H, int ds, int n, int dtype, void* stream);
 // products over groups: per-head matrices, routed experts (grouped_gemm.cu)
 int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const void* A, int64_t lda, int64_t a_group_cols,
                      const int* a_rows, const void* W, const void* W2, int64_t w_group_stride, int64_t ldw, const int* seg,

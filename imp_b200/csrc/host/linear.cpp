@@ -57,6 +57,15 @@ void swiglu(Runtime& rt, Tensor out, const Tensor& gate_up, int interleave) {
     check_launch(imp_swiglu(out.data, gate_up.data, (int)rows(out), (int)cols(out), interleave, out.dtype, rt.stream), "swiglu");
 }
 
+void gated_act(Runtime& rt, Tensor out, const Tensor& gate_up, int interleave, int act) {
+    if (act == 0) return swiglu(rt, out, gate_up, interleave);
+    need(cols(gate_up) == 2 * cols(out) && rows(gate_up) == rows(out) && gate_up.dtype == out.dtype && contiguous(out) &&
+             contiguous(gate_up),
+         "gated_act: gate_up must be [T, 2F] beside out [T, F], both dense");
+    ++rt.launches;
+    check_launch(imp_gated_act(out.data, gate_up.data, (int)rows(out), (int)cols(out), interleave, act, out.dtype, rt.stream), "gated_act");
+}
+
 void embedding(Runtime& rt, Tensor out, const Tensor& table, const int32_t* ids, int n, float scale) {
     need(out.dtype == F32 && contiguous(out) && rows(out) == n && cols(out) == cols(table) && contiguous(table),
          "embedding: out must be dense float32 [T, d] and the table dense [vocab, d]");
@@ -243,6 +252,15 @@ void linear_swiglu(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w) {
     Tensor gu = rt.empty(M, 2 * F, x.dtype);
     linear(rt, gu, x, w);
     swiglu(rt, out, gu, SWIGLU_INTERLEAVE);
+}
+
+void linear_gated(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w, int act) {
+    if (act == 0) return linear_swiglu(rt, out, x, w);
+    const int64_t M = M_of(x), F = cols(out);
+    if (M == 0) return;
+    Tensor gu = rt.empty(M, 2 * F, x.dtype);
+    linear(rt, gu, x, w);
+    gated_act(rt, out, gu, SWIGLU_INTERLEAVE, act);
 }
 
 // ---------------------------------------------------------------------------------------- norm

@@ -415,13 +415,16 @@ Tensor DeviceModel::forward(Step& st) {
         IMP_CUDA(cudaMemcpyAsync(st.embedding_out.data, h.data, (size_t)numel(h) * elem_size(h.dtype), cudaMemcpyDeviceToDevice, rt_->stream));
     }
     Branch pending;
+    st.stream_copy = Tensor{};
     for (size_t j = 0; j < order_.size(); ++j) {
         rt_->arena->next_layer();
         st.layer = order_[j];
+        const void* copy_before = st.stream_copy.data;
         // one mixer: its cache, or null when it has none; several: the array of their caches in slot order
         LayerCache* lc = &layer_caches_[(size_t)cache_first_[j]];
         if (cache_count_[j] == 1 && !lc->view.kind) lc = nullptr;
         pending = blocks_[(size_t)order_[j]]->forward(st, h, pending, lc);
+        if (st.stream_copy.data == copy_before) st.stream_copy = Tensor{};   // the block left no copy of its own: the old one is stale
         if (diag_ && !diag_->dump_dir.empty()) diag_->dump_stream(st, (int)j, h, pending);
     }
     st.layer = -1;

@@ -28,6 +28,9 @@ Tensor cat_rows(Runtime& rt, WeightStore& store, const std::vector<Tensor>& part
 Tensor to_float32(Runtime& rt, WeightStore& store, const Tensor& t);   // a 32-bit copy of a small weight
 
 void swiglu(Runtime& rt, Tensor out, const Tensor& gate_up, int interleave);
+// The same with the activation chosen: act 0 silu, 1 gelu (tanh form).
+void gated_act(Runtime& rt, Tensor out, const Tensor& gate_up, int interleave, int act);
+void linear_gated(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w_interleaved, int act);
 void cast(Runtime& rt, Tensor dst, const Tensor& src);
 
 // The tensor a branch stands for (runs the summing kernel if its parts are still apart).

@@ -224,6 +224,10 @@ static void copy_out(Step& st, const Tensor& produced, ImpTensor& out) {
 void Norm::call(Step& st, ImpCall& c) {
     copy_out(st, add_norm(st, c.h, branch_of(c.branch), c.rows, c.rows ? c.n_rows : 0), c.out);
 }
+Tensor Norm::add_norm_store(Step&, Tensor, float, const Branch&) {
+    fail(IMP_ERROR_UNSUPPORTED, "this norm cannot store its result as the stream");
+    return Tensor{};
+}
 void Position::apply(Step&, Tensor, Tensor) { fail(IMP_ERROR_UNSUPPORTED, "this position encoding has no unfused path"); }
 void Position::call(Step& st, ImpCall& c) { apply(st, c.q, c.k); }
 void Mixer::call(Step& st, ImpCall& c) {

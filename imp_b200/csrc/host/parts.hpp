@@ -88,6 +88,8 @@ struct Step {
     struct Diagnostics* diag = nullptr;        // stage timers / statistics when a debugging switch is set
     int layer = -1;                            // index of the layer that is running (for stage names)
     Tensor embedding_out{};                    // a copy of the embedding's output, kept when a block asks for it (Block::wants_embedding)
+    Tensor stream_copy{};                      // the stream in the activation type, when the block that just ran left one (post-norm
+                                               // blocks: their last norm writes it beside the 32-bit stream); else null
     int context = 0;                           // the sequences' mean length after this step, rounded to a power of two: what
                                                // launch choices may depend on (a decode graph is kept per batch size and context)
     int T() const { return view.n_tokens; }
@@ -137,6 +139,10 @@ struct Norm : Part {
     virtual bool takes_split_sum() const { return false; }
     virtual bool takes_column_scale() const { return false; }   // multiplies a branch's col_scale in while adding
     virtual Tensor add_norm(Step& st, Tensor h, const Branch& branch, const int32_t* rows = nullptr, int n_rows = 0) = 0;
+    // Post-norm: h <- norm(h_mult * h + branch), the normalised sum stored as the stream (32-bit); returns its copy in
+    // the activation type.  Only norms that say stores_stream() implement it.
+    virtual bool stores_stream() const { return false; }
+    virtual Tensor add_norm_store(Step& st, Tensor h, float h_mult, const Branch& branch);
     void call(Step& st, ImpCall& c) override;
 };
 
@@ -246,6 +252,7 @@ const PartClass& part_class(const std::string& category, const std::string& kind
 std::vector<std::string> known_parts(const std::string& category);
 void ensure_builtin_parts();   // registers the library's own kinds once
 void register_mixer_parts();    // parts_mixers.cpp: the kinds beyond plain attention (called by ensure_builtin_parts)
+void register_recurrent_parts();   // parts_recurrent.cpp: retention, the delta rules over the general scan, attention with gated heads, the post-norm block
 void register_routed_parts();   // parts_routed.cpp: layer norm, latent attention, wkv, routed experts, blocks with scaled branches
 
 // Builds parts and owns them.  Parts without tensors are shared between equal specs.

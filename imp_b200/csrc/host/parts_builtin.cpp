@@ -204,11 +204,13 @@ struct GQAAttention : Mixer {
 };
 
 // ------------------------------------------------------------------------------- feed-forward
-// down( silu(x Wg^T) * (x Wu^T) ), activation in 32-bit (src/graph/executor_forward.cu:933-951,
-// 1124-1140; src/compute/activation.cu:67-87).  params: hidden_size, intermediate_size.
+// down( act(x Wg^T) * (x Wu^T) ), activation in 32-bit (src/graph/executor_forward.cu:933-951,
+// 1124-1140; src/compute/activation.cu:67-87).  params: hidden_size, intermediate_size, activation ("silu", the default,
+// or "gelu_tanh": 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  Registered as "swiglu" and as "gated_mlp".
 struct SwiGLU : FeedForward {
     int64_t f;
     bool interleaved;
+    int act = 0;   // 0 silu, 1 gelu (tanh form)
     Tensor w_gu, w_down;
     static TensorSpecs specs(const Json& p) {
         const int64_t d = need_int(p, "hidden_size", "swiglu"), f = need_int(p, "intermediate_size", "swiglu");
@@ -220,6 +222,9 @@ struct SwiGLU : FeedForward {
     }
     explicit SwiGLU(BuildArgs& a) {
         f = need_int(a.params, "intermediate_size", "swiglu");
+        const std::string an = a.params.get_string("activation", "silu");
+        if (an != "silu" && an != "gelu_tanh") fail(IMP_ERROR_INVALID_MODEL, "gated feed-forward: unknown activation '" + an + "' (known: silu, gelu_tanh)");
+        act = an == "silu" ? 0 : 1;
         Runtime& rt = *a.rt;
         Tensor gate = a.tensor("gate_proj"), up = a.tensor("up_proj");
         // Gate and up rows alternate in runs of 8 so that one kernel can produce the activation from the fused
@@ -234,16 +239,16 @@ struct SwiGLU : FeedForward {
     Branch forward(Step& st, Tensor x) override {
         Runtime& rt = *st.rt;
         const int64_t T = rows(x);
-        Tensor act = rt.empty(T, f);
+        Tensor hid = rt.empty(T, f);
         if (interleaved) {
-            if (!rt.without('g')) linear_swiglu(rt, act, x, w_gu);
+            if (!rt.without('g')) linear_gated(rt, hid, x, w_gu, act);
         } else {
             Tensor gu = rt.empty(T, 2 * f);
             linear(rt, gu, x, w_gu);
-            swiglu(rt, act, gu, 0);
+            gated_act(rt, hid, gu, 0, act);
         }
         if (rt.without('d')) return Branch::of(rt.empty(T, rows(w_down)));
-        return linear(rt, rt.empty(T, rows(w_down)), act, w_down, defer_out);
+        return linear(rt, rt.empty(T, rows(w_down)), hid, w_down, defer_out);
     }
 };
 
@@ -346,6 +351,7 @@ void ensure_builtin_parts() {
         attn.cache_spec = &GQAAttention::cache;
         register_part_class("mixer", "gqa_attention", attn, true);
         register_part_class("feed_forward", "swiglu", simple_class<SwiGLU>(&SwiGLU::specs), true);
+        register_part_class("feed_forward", "gated_mlp", simple_class<SwiGLU>(&SwiGLU::specs), true);
         PartClass block = simple_class<PreNormBlock>(nullptr);
         block.part_slots = &PreNormBlock::slots;
         register_part_class("block", "prenorm", block, true);
@@ -353,6 +359,7 @@ void ensure_builtin_parts() {
         register_part_class("head", "linear_head", simple_class<LinearHead>(&LinearHead::specs), true);
         register_mixer_parts();
         register_routed_parts();
+        register_recurrent_parts();
     });
 }
 

@@ -33,13 +33,34 @@ Branch parts_summed(Runtime& rt, const Branch& b) {
 }
 
 // -------------------------------------------------------------------------------------------- layer norm
-// y = (x - mean) / sqrt(var + eps) * w over the last axis, the variance being the mean of the squared deviations; a
-// weight and no bias.  Statistics in 32-bit.  params: size, eps.
+// y = (x - mean) / sqrt(var + eps) * w (+ b) over the last axis, the variance being the mean of the squared deviations; a
+// weight and, with `bias`, a bias.  Statistics in 32-bit.  It can store its result as the stream (post-norm blocks).
+// params: size, eps, bias (default false).
 struct LayerNorm : Norm {
-    Tensor weight;
+    Tensor weight, bias{};
     float eps;
-    explicit LayerNorm(BuildArgs& a) : weight(a.tensor("weight")), eps((float)a.params.get_double("eps", 1e-5)) {}
+    explicit LayerNorm(BuildArgs& a) : weight(a.tensor("weight")), eps((float)a.params.get_double("eps", 1e-5)) {
+        if (a.params.get_bool("bias", false)) {
+            bias = a.tensor("bias");
+            if (bias.dtype != weight.dtype || numel(bias) != numel(weight)) fail(IMP_ERROR_INVALID_MODEL, "layernorm: weight and bias must agree in type and size");
+        }
+    }
     bool takes_column_scale() const override { return true; }
+    bool stores_stream() const override { return true; }
+    Tensor add_norm_store(Step& st, Tensor h, float h_mult, const Branch& branch) override {
+        Runtime& rt = *st.rt;
+        const int d = (int)cols(h);
+        Tensor out = rt.empty(rows(h), d);
+        if (h.dtype != F32 || !contiguous(h) || numel(weight) != d) fail(IMP_ERROR_INVALID_ARG, "layernorm: the stream must be dense float32 [T, d], the weight [d]");
+        const Branch b = parts_summed(rt, branch);
+        if (!b.empty() && (rows(b.t) != rows(h) || cols(b.t) != d || b.t.dtype != out.dtype || !contiguous(b.t)))
+            fail(IMP_ERROR_INVALID_ARG, "layernorm: the branch must be dense, of the stream's shape and the output's type");
+        ++rt.launches;
+        check_launch(imp_add_layernorm_ex((float*)h.data, h_mult, b.empty() ? nullptr : b.t.data, b.col_scale, weight.data, bias.data, out.data, nullptr,
+                                          (int)rows(h), d, eps, out.dtype, weight.dtype, 2, rt.stream),
+                     "add_layernorm");
+        return out;
+    }
     Tensor add_norm(Step& st, Tensor h, const Branch& branch, const int32_t* rows_idx, int n_rows) override {
         Runtime& rt = *st.rt;
         const int64_t n = rows_idx ? n_rows : rows(h);
@@ -50,8 +71,8 @@ struct LayerNorm : Norm {
         if (!b.empty() && (rows(b.t) != rows(h) || cols(b.t) != d || b.t.dtype != out.dtype || !contiguous(b.t)))
             fail(IMP_ERROR_INVALID_ARG, "layernorm: the branch must be dense, of the stream's shape and the output's type");
         ++rt.launches;
-        check_launch(imp_add_layernorm((float*)h.data, b.empty() ? nullptr : b.t.data, b.col_scale, weight.data, out.data, rows_idx, (int)n, d, eps,
-                                       out.dtype, weight.dtype, rows_idx ? 0 : 1, rt.stream),
+        check_launch(imp_add_layernorm_ex((float*)h.data, 1.f, b.empty() ? nullptr : b.t.data, b.col_scale, weight.data, bias.data, out.data, rows_idx,
+                                          (int)n, d, eps, out.dtype, weight.dtype, rows_idx ? 0 : 1, rt.stream),
                      "add_layernorm");
         return out;
     }
@@ -582,6 +603,7 @@ void register_routed_parts() {
     norm.tensor_specs = [](const Json& p) {
         TensorSpecs s;
         s.emplace_back("weight", TensorSpec{{need_int(p, "size", "layernorm")}, "norm", "one_plus_normal"});
+        if (p.get_bool("bias", false)) s.emplace_back("bias", TensorSpec{{need_int(p, "size", "layernorm")}, "vector", "normal"});
         return s;
     };
     register_part_class("norm", "layernorm", norm, true);

@@ -1,8 +1,11 @@
-// Layer norm with a weight and no bias, fused with the residual sum, and the small kernels that go
+// Layer norm with a weight and an optional bias, fused with the residual sum, and the small kernels that go
 // with a stream whose branches carry a factor per column.
 //
-//   h += s (.) branch            (s: 32-bit factor per column, optional; branch optional)
-//   y  = (h - mean(h)) / sqrt(var(h) + eps) * w,   var = mean((h - mean)^2)
+//   h  = m h + s (.) branch      (m: a constant, 1 unless given; s: 32-bit factor per column, optional; branch optional)
+//   y  = (h - mean(h)) / sqrt(var(h) + eps) * w (+ b),   var = mean((h - mean)^2)
+//
+// write_h: 0 leaves the stream as it is, 1 stores the sum (pre-norm: the stream is the sum), 2 stores y in 32-bit
+// (post-norm: the normalised sum is the stream).
 //
 // The residual stream is 32-bit; mean, variance and the scaling are 32-bit.  One block per row with a
 // fixed block size; the row is held in registers between the passes (up to LN_MAX_PER_THREAD values a
@@ -16,7 +19,7 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restrict__ h, const TA* __restrict__ branch,
                                                                  const float* __restrict__ col_scale, const TW* __restrict__ w,
                                                                  TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
-                                                                 int write_h) {
+                                                                 int write_h, float h_mult, const TW* __restrict__ bias) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float scratch[33];
@@ -31,17 +34,17 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restri
         const int i = threadIdx.x + e * LN_BLOCK;
         float v = 0.f;
         if (i < d) {
-            v = hrow[i];
+            v = hrow[i] * h_mult;
             if (brow) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
-            if (write_h && brow) hrow[i] = v;
+            if (write_h == 1 && brow) hrow[i] = v;
         }
         keep[e] = v;
         sum += v;
     }
     for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
-        float v = hrow[i];
+        float v = hrow[i] * h_mult;
         if (brow) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
-        if (write_h && brow) hrow[i] = v;
+        if (write_h == 1 && brow) hrow[i] = v;
         sum += v;
     }
     const float mean = block_sum(sum, scratch) / (float)d;
@@ -54,9 +57,9 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restri
             ss = fmaf(c, c, ss);
         }
     }
-    const bool stored = write_h && brow;   // beyond the kept part the row is read again: from h if it was stored, else recomputed
+    const bool stored = write_h == 1 && brow;   // beyond the kept part the row is read again: from h if it was stored, else recomputed
     for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
-        float v = hrow[i];
+        float v = stored ? hrow[i] : hrow[i] * h_mult;
         if (brow && !stored) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
         const float c = v - mean;
         ss = fmaf(c, c, ss);
@@ -66,12 +69,20 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_kernel(float* __restri
 #pragma unroll
     for (int e = 0; e < LN_KEEP; ++e) {
         const int i = threadIdx.x + e * LN_BLOCK;
-        if (i < d) orow[i] = from_float<TA>((keep[e] - mean) * inv * to_float(w[i]));
+        if (i < d) {
+            const float y = fmaf((keep[e] - mean) * inv, to_float(w[i]), bias ? to_float(bias[i]) : 0.f);
+            orow[i] = from_float<TA>(y);
+            if (write_h == 2) hrow[i] = y;
+        }
     }
+    // the part of the row that is read again is normalised in place only after every thread has read what it needs:
+    // each thread rewrites the entries it alone reads
     for (int i = threadIdx.x + LN_KEEP * LN_BLOCK; i < d; i += LN_BLOCK) {
-        float v = hrow[i];
+        float v = stored ? hrow[i] : hrow[i] * h_mult;
         if (brow && !stored) v = col_scale ? fmaf(col_scale[i], to_float(brow[i]), v) : v + to_float(brow[i]);
-        orow[i] = from_float<TA>((v - mean) * inv * to_float(w[i]));
+        const float y = fmaf((v - mean) * inv, to_float(w[i]), bias ? to_float(bias[i]) : 0.f);
+        orow[i] = from_float<TA>(y);
+        if (write_h == 2) hrow[i] = y;
     }
 }
 
@@ -102,7 +113,7 @@ template <typename TA, typename TW, int NV>
 __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch,
                                                                      const float* __restrict__ col_scale, const TW* __restrict__ w,
                                                                      TA* __restrict__ out, const int* __restrict__ rows, int d, float eps,
-                                                                     int write_h) {
+                                                                     int write_h, float h_mult, const TW* __restrict__ bias) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float scratch[33];
@@ -115,6 +126,7 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_vec_kernel(float* __re
     for (int e = 0; e < NV; ++e) {
         const int i = (threadIdx.x + e * LN_BLOCK) * 4;
         v[e] = i < d ? Vec4<float>::load(hrow + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[e].x *= h_mult, v[e].y *= h_mult, v[e].z *= h_mult, v[e].w *= h_mult;
     }
     if (brow) {
 #pragma unroll
@@ -128,7 +140,7 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_vec_kernel(float* __re
                 } else {
                     v[e].x += b.x, v[e].y += b.y, v[e].z += b.z, v[e].w += b.w;
                 }
-                if (write_h) Vec4<float>::store(hrow + i, v[e]);
+                if (write_h == 1) Vec4<float>::store(hrow + i, v[e]);
             }
         }
     }
@@ -152,48 +164,59 @@ __global__ void __launch_bounds__(LN_BLOCK) add_layernorm_vec_kernel(float* __re
         const int i = (threadIdx.x + e * LN_BLOCK) * 4;
         if (i < d) {
             const float4 ww = Vec4<TW>::load(w + i);
-            Vec4<TA>::store(orow + i, make_float4((v[e].x - mean) * inv * ww.x, (v[e].y - mean) * inv * ww.y, (v[e].z - mean) * inv * ww.z,
-                                                  (v[e].w - mean) * inv * ww.w));
+            const float4 bb = bias ? Vec4<TW>::load(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 y = make_float4(fmaf((v[e].x - mean) * inv, ww.x, bb.x), fmaf((v[e].y - mean) * inv, ww.y, bb.y),
+                                         fmaf((v[e].z - mean) * inv, ww.z, bb.z), fmaf((v[e].w - mean) * inv, ww.w, bb.w));
+            Vec4<TA>::store(orow + i, y);
+            if (write_h == 2) Vec4<float>::store(hrow + i, y);
         }
     }
 }
 
 template <typename TA, typename TW>
 static cudaError_t launch_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows, int n, int d,
-                                    float eps, int write_h, cudaStream_t s) {
+                                    float eps, int write_h, float h_mult, const void* bias_v, cudaStream_t s) {
+    const TW* bias = (const TW*)bias_v;
     const dim3 grid(n), block(LN_BLOCK);
     const bool vec = d % 4 == 0 && d <= LN_BLOCK * 4 * 8 && (uintptr_t)h % 16 == 0 && (uintptr_t)branch % 8 == 0 && (uintptr_t)out % 8 == 0 &&
-                     (uintptr_t)w % 16 == 0 && (uintptr_t)col_scale % 16 == 0;
+                     (uintptr_t)w % 16 == 0 && (uintptr_t)col_scale % 16 == 0 && (uintptr_t)bias_v % 16 == 0;
     if (vec) {
         const int nv = (d / 4 + LN_BLOCK - 1) / LN_BLOCK;
-        if (nv <= 1) return imp_launch(add_layernorm_vec_kernel<TA, TW, 1>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
-        if (nv <= 2) return imp_launch(add_layernorm_vec_kernel<TA, TW, 2>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
-        if (nv <= 4) return imp_launch(add_layernorm_vec_kernel<TA, TW, 4>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
-        return imp_launch(add_layernorm_vec_kernel<TA, TW, 8>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+        if (nv <= 1) return imp_launch(add_layernorm_vec_kernel<TA, TW, 1>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h, h_mult, bias);
+        if (nv <= 2) return imp_launch(add_layernorm_vec_kernel<TA, TW, 2>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h, h_mult, bias);
+        if (nv <= 4) return imp_launch(add_layernorm_vec_kernel<TA, TW, 4>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h, h_mult, bias);
+        return imp_launch(add_layernorm_vec_kernel<TA, TW, 8>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h, h_mult, bias);
     }
-    return imp_launch(add_layernorm_kernel<TA, TW>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h);
+    return imp_launch(add_layernorm_kernel<TA, TW>, grid, block, 0, s, h, (const TA*)branch, col_scale, (const TW*)w, (TA*)out, rows, d, eps, write_h, h_mult, bias);
 }
 
-// h: [*, d] float32 stream; branch (optional, dense [*, d] of the activation type) is added first, times col_scale
-// (optional float32 [d]).  rows: optional gather list (then h is left as it is: write_h must be 0).
-IMP_API int imp_add_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows,
-                              int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream) {
+// h: [*, d] float32 stream, taken times h_mult; branch (optional, dense [*, d] of the activation type) is added, times
+// col_scale (optional float32 [d]).  bias: optional, of the weight's type.  rows: optional gather list (then h is left as it
+// is: write_h must be 0).  write_h: 1 stores the sum in h, 2 stores the normalised result in h.
+IMP_API int imp_add_layernorm_ex(float* h, float h_mult, const void* branch, const float* col_scale, const void* w, const void* bias, void* out,
+                                 const int* rows, int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream) {
     if (n_out_rows == 0) return 0;
-    IMP_CHECK_ARG(h && w && out && d > 0 && n_out_rows > 0, "imp_add_layernorm: bad argument");
+    IMP_CHECK_ARG(h && w && out && d > 0 && n_out_rows > 0 && write_h >= 0 && write_h <= 2, "imp_add_layernorm: bad argument");
     IMP_CHECK_ARG(!(rows && write_h), "imp_add_layernorm: a gather list and write_h exclude each other");
+    IMP_CHECK_ARG(write_h != 1 || h_mult == 1.f || branch, "imp_add_layernorm: a scaled stream is stored with its branch only");
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (act_dtype == IMP_F32)
-        e = w_dtype == IMP_F32 ? launch_layernorm<float, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s)
-                               : launch_layernorm<float, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s);
+        e = w_dtype == IMP_F32 ? launch_layernorm<float, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, h_mult, bias, s)
+                               : launch_layernorm<float, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, h_mult, bias, s);
     else
-        e = w_dtype == IMP_F32 ? launch_layernorm<__nv_bfloat16, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s)
-                               : launch_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, s);
+        e = w_dtype == IMP_F32 ? launch_layernorm<__nv_bfloat16, float>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, h_mult, bias, s)
+                               : launch_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, col_scale, w, out, rows, n_out_rows, d, eps, write_h, h_mult, bias, s);
     if (e != cudaSuccess) {
         imp_set_error("imp_add_layernorm: %s", cudaGetErrorString(e));
         return (int)e;
     }
     return 0;
+}
+
+IMP_API int imp_add_layernorm(float* h, const void* branch, const float* col_scale, const void* w, void* out, const int* rows,
+                              int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream) {
+    return imp_add_layernorm_ex(h, 1.f, branch, col_scale, w, nullptr, out, rows, n_out_rows, d, eps, act_dtype, w_dtype, write_h ? 1 : 0, stream);
 }
 
 // x[r][c] *= s[c], the product made in 32-bit.

@@ -1,0 +1,279 @@
+// Between a q,k,v product and the paged attention kernels, for attention whose heads are normalised, rotated in
+// part, scaled per head and whose values are normalised; and the small kernels of blocks that combine two mixers
+// or gate their heads.
+//
+//   qkv_prepare      per token: q heads  -> RMS norm with a weight shared by the heads (optional), rotation of the
+//                    first `rot` entries (pairs i, i + rot/2), times a number per head (optional) -> q_out, padded
+//                    to the cache's head size; k heads -> norm, rotation -> K page; v heads -> divided by their
+//                    root mean square (optional) -> V page.  Key and value heads may have different sizes: the
+//                    cache's head size is the larger one, the rest of a row is zeros.
+//   head_gate        y[t, h, :] *= sigmoid(g[t, h])
+//   rms_pair_mean    out = ca * a / rms(a) * wa + cb * b / rms(b) * wb   (two branch outputs, each normalised over the width)
+//   gated_act        out = act(gate) * up for gelu (tanh form) and silu over [gate | up] rows
+//   act_rows         out[t, :] = act(x[t, c0 : c0 + n])  (a slice of a product's rows made dense, tanh or identity)
+// Norm statistics, angles, the rotation and the per-head factors are 32-bit; results are rounded once.
+#include "common.cuh"
+
+constexpr int QP_BLOCK = 128;
+constexpr int QP_MAX_D = 512;
+constexpr int QP_PER = QP_MAX_D / 32;
+
+// One warp per (token, unit); units: Hq query heads, then Hkv key heads, then Hkv value heads.
+// proj: [T, ld] with columns [q: Hq*D | k: Hkv*D | v: Hkv*Dv | ...].  inv_freq: [rot/2] float32 (angle = pos * inv_freq[i]).
+template <typename TA>
+__global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
+    const TA* __restrict__ proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, float eps, int v_norm, const float* __restrict__ inv_freq, int rot,
+    const float* __restrict__ head_mult, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int bt_stride, int n_seqs, TA* __restrict__ q_out, int64_t q_ld, TA* __restrict__ k_cache,
+    TA* __restrict__ v_cache, int page_size, int num_pages, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float rot_s[QP_BLOCK / 32][QP_MAX_D];
+    const int lane = threadIdx.x & 31;
+    const int units = Hq + 2 * Hkv;
+    const int64_t item = (int64_t)blockIdx.x * (QP_BLOCK / 32) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * units) return;
+    const int64_t t = item / units;
+    const int unit = (int)(item - t * units);
+    const int seq = seq_of_token[t], pos = positions[t];
+    if (seq < 0 || seq >= n_seqs || pos < 0 || pos / page_size >= bt_stride) {
+        if (lane == 0 && unit == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        return;
+    }
+    const bool is_q = unit < Hq, is_v = unit >= Hq + Hkv;
+    const int head = is_q ? unit : is_v ? unit - Hq - Hkv : unit - Hq;
+    const int n = is_v ? Dv : D;
+    const TA* src = proj + t * ld + (is_q ? (int64_t)head * D : is_v ? (int64_t)Hq * D + (int64_t)Hkv * D + (int64_t)head * Dv
+                                                                     : (int64_t)Hq * D + (int64_t)head * D);
+    TA* dst;
+    if (is_q) {
+        dst = q_out + t * q_ld + (int64_t)head * Dc;
+    } else {
+        const int page = block_table[(int64_t)seq * bt_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0) imp_report(status, IMP_BAD_PAGE);
+            return;
+        }
+        TA* cache = is_v ? v_cache : k_cache;
+        if (!cache) return;
+        dst = cache + (((int64_t)page * Hkv + head) * page_size + pos % page_size) * Dc;   // pages are [page][kv head][slot][entry]
+    }
+    float x[QP_PER], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < QP_PER; ++i) {
+        const int d = lane + i * 32;
+        x[i] = d < n ? to_float(src[d]) : 0.f;
+        ss = fmaf(x[i], x[i], ss);
+    }
+    const float* nw = is_q ? q_norm_w : is_v ? nullptr : k_norm_w;
+    const bool normed = is_v ? v_norm != 0 : nw != nullptr;
+    if (normed) {
+        ss = warp_sum(ss);
+        const float r = rsqrtf(ss / (float)n + eps);
+#pragma unroll
+        for (int i = 0; i < QP_PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < n) x[i] = x[i] * r * (nw ? nw[d] : 1.f);
+        }
+    }
+    if (!is_v && rot > 0) {
+        // entry d < rot/2 pairs with d + rot/2, which another lane holds: the head goes through shared memory once
+        float* row = rot_s[threadIdx.x >> 5];
+        const int half = rot / 2;
+#pragma unroll
+        for (int i = 0; i < QP_PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < rot) row[d] = x[i];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < QP_PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < rot) {
+                const int fi = d < half ? d : d - half;
+                const float partner = row[d < half ? d + half : d - half];
+                float sn, cs;
+                sincosf((float)pos * inv_freq[fi], &sn, &cs);
+                // (u, v) -> (u cos - v sin, v cos + u sin)
+                x[i] = d < half ? x[i] * cs - partner * sn : x[i] * cs + partner * sn;
+            }
+        }
+    }
+    const float mult = (is_q && head_mult) ? head_mult[head] : 1.f;
+#pragma unroll
+    for (int i = 0; i < QP_PER; ++i) {
+        const int d = lane + i * 32;
+        if (d < Dc) dst[d] = from_float<TA>(d < n ? x[i] * mult : 0.f);
+    }
+}
+
+// y[t, h, :] *= sigmoid(g[t, h]); a warp per (token, head).
+template <typename TA>
+__global__ void head_gate_kernel(TA* __restrict__ y, int64_t y_ld, const TA* __restrict__ g, int64_t g_ld, int n_tokens, int H, int Dv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * H) return;
+    const int64_t t = item / H;
+    const int h = (int)(item - t * H);
+    const float s = 1.f / (1.f + expf(-to_float(g[t * g_ld + h])));
+    TA* row = y + t * y_ld + (int64_t)h * Dv;
+    for (int d = lane; d < Dv; d += 32) row[d] = from_float<TA>(to_float(row[d]) * s);
+}
+
+// out[r] = ca * a[r] / rms(a[r]) * wa + cb * b[r] / rms(b[r]) * wb; one block per row, the two sums of squares in 32-bit.
+template <typename TA>
+__global__ void __launch_bounds__(256) rms_pair_mean_kernel(TA* __restrict__ out, const TA* __restrict__ a, const float* __restrict__ wa, float ca,
+                                                            const TA* __restrict__ b, const float* __restrict__ wb, float cb, int d, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int64_t r = blockIdx.x;
+    const TA* ar = a + r * d;
+    const TA* br = b + r * d;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float x = to_float(ar[i]), y = to_float(br[i]);
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    const float ra = rsqrtf(block_sum(sa, scratch) / (float)d + eps) * ca;
+    const float rb = rsqrtf(block_sum(sb, scratch) / (float)d + eps) * cb;
+    TA* o = out + r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TA>(fmaf(to_float(ar[i]) * ra, wa[i], to_float(br[i]) * rb * wb[i]));
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// out[t, f] = act(gate) * up over rows [gate | up] (block == 0) or runs of `block` gate entries followed by their up entries.
+// act: 0 silu, 1 gelu (tanh form).
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_tokens, int F, int block, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = n_tokens * (int64_t)F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / F;
+        const int f = (int)(i - t * F);
+        const int gi = block ? (f / block) * 2 * block + f % block : f;
+        const int ui = block ? gi + block : F + f;
+        const float g = to_float(gu[t * 2 * F + gi]);
+        const float u = to_float(gu[t * 2 * F + ui]);
+        const float a = act == 0 ? g / (1.f + expf(-g)) : gelu_tanh_f(g);
+        out[i] = from_float<T>(a * u);
+    }
+}
+
+// out[t, j] = act(x[t, j]) for j < n: a dense copy of a slice of wider rows.  act: 0 identity, 1 tanh.
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t ld, int64_t n_tokens, int n, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = n_tokens * (int64_t)n;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / n;
+        const float v = to_float(x[t * ld + (i - t * n)]);
+        out[i] = from_float<T>(act == 1 ? tanhf(v) : v);
+    }
+}
+
+IMP_API int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
+                            const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, const float* head_mult,
+                            const int* positions, const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* q_out,
+                            int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype, int* status,
+                            void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(proj && positions && seq_of_token && block_table && q_out, "imp_qkv_prepare: null pointer");
+    IMP_CHECK_ARG(Hq > 0 && Hkv > 0 && D > 0 && Dv > 0 && Dc >= D && Dc >= Dv && Dc <= QP_MAX_D,
+                  "imp_qkv_prepare: head sizes %d / %d must fit the cache's %d (at most %d)", D, Dv, Dc, QP_MAX_D);
+    IMP_CHECK_ARG(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "imp_qkv_prepare: the rotated part must be even and within the head");
+    IMP_CHECK_ARG((q_norm_w == nullptr) == (k_norm_w == nullptr), "imp_qkv_prepare: q and k are normalised together or not at all");
+    IMP_CHECK_ARG(ld >= (int64_t)(Hq + Hkv) * D + (int64_t)Hkv * Dv && q_ld >= (int64_t)Hq * Dc, "imp_qkv_prepare: rows too short");
+    IMP_CHECK_ARG(page_size > 0 && num_pages > 0, "imp_qkv_prepare: bad cache geometry");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t items = (int64_t)n_tokens * (Hq + 2 * Hkv);
+    const dim3 grid((unsigned)((items + QP_BLOCK / 32 - 1) / (QP_BLOCK / 32)));
+    if (act_dtype == IMP_F32)
+        imp_launch(qkv_prepare_kernel<float>, grid, dim3(QP_BLOCK), 0, s, (const float*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w, k_norm_w, eps,
+                   v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (float*)q_out, q_ld, (float*)k_cache,
+                   (float*)v_cache, page_size, num_pages, status);
+    else
+        imp_launch(qkv_prepare_kernel<__nv_bfloat16>, grid, dim3(QP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w,
+                   k_norm_w, eps, v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (__nv_bfloat16*)q_out,
+                   q_ld, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, num_pages, status);
+    IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_head_gate(void* y, int64_t y_ld, const void* g, int64_t g_ld, int n_tokens, int H, int Dv, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(y && g && H > 0 && Dv > 0 && y_ld >= (int64_t)H * Dv && g_ld >= H, "imp_head_gate: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t items = (int64_t)n_tokens * H;
+    const dim3 grid((unsigned)((items + 7) / 8));
+    if (dtype == IMP_F32) imp_launch(head_gate_kernel<float>, grid, dim3(256), 0, s, (float*)y, y_ld, (const float*)g, g_ld, n_tokens, H, Dv);
+    else imp_launch(head_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)y, y_ld, (const __nv_bfloat16*)g, g_ld, n_tokens, H, Dv);
+    IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_rms_pair_mean(void* out, const void* a, const float* wa, float ca, const void* b, const float* wb, float cb, int n_rows, int d,
+                              float eps, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(out && a && b && wa && wb && d > 0, "imp_rms_pair_mean: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IMP_F32)
+        imp_launch(rms_pair_mean_kernel<float>, dim3(n_rows), dim3(256), 0, s, (float*)out, (const float*)a, wa, ca, (const float*)b, wb, cb, d, eps);
+    else
+        imp_launch(rms_pair_mean_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, wa, ca,
+                   (const __nv_bfloat16*)b, wb, cb, d, eps);
+    IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_gated_act(void* out, const void* gate_up, int n_tokens, int F, int block, int act, int dtype, void* stream) {
+    if (n_tokens == 0 || F == 0) return 0;
+    IMP_CHECK_ARG(out && gate_up && n_tokens > 0 && F > 0 && block >= 0 && (block == 0 || F % block == 0) && (act == 0 || act == 1),
+                  "imp_gated_act: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)n_tokens * F;
+    const dim3 grid((unsigned)std::min<int64_t>((total + 255) / 256, 65535));
+    if (dtype == IMP_F32) imp_launch(gated_act_kernel<float>, grid, dim3(256), 0, s, (float*)out, (const float*)gate_up, (int64_t)n_tokens, F, block, act);
+    else imp_launch(gated_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, (int64_t)n_tokens, F, block, act);
+    IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_act_rows(void* out, const void* x, int64_t ld, int n_tokens, int n, int act, int dtype, void* stream) {
+    if (n_tokens == 0 || n == 0) return 0;
+    IMP_CHECK_ARG(out && x && n > 0 && ld >= n && (act == 0 || act == 1), "imp_act_rows: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)n_tokens * n;
+    const dim3 grid((unsigned)std::min<int64_t>((total + 255) / 256, 65535));
+    if (dtype == IMP_F32) imp_launch(act_rows_kernel<float>, grid, dim3(256), 0, s, (float*)out, (const float*)x, ld, (int64_t)n_tokens, n, act);
+    else imp_launch(act_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, ld, (int64_t)n_tokens, n, act);
+    IMP_RETURN_LAUNCH();
+}
+
+// dst[t, h, 0:n] = src[t, h, 0:n] out of heads of `ds` entries: the heads' first n columns as dense rows.
+template <typename T>
+__global__ void gather_head_cols_kernel(T* __restrict__ dst, const T* __restrict__ src, int64_t n_tokens, int H, int ds, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t total = n_tokens * (int64_t)H * n;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t th = i / n;
+        dst[i] = src[th * ds + (i - th * n)];
+    }
+}
+
+IMP_API int imp_gather_head_cols(void* dst, const void* src, int n_tokens, int H, int ds, int n, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(dst && src && H > 0 && n > 0 && ds >= n, "imp_gather_head_cols: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t total = (int64_t)n_tokens * H * n;
+    const dim3 grid((unsigned)std::min<int64_t>((total + 255) / 256, 65535));
+    if (dtype == IMP_F32) imp_launch(gather_head_cols_kernel<float>, grid, dim3(256), 0, s, (float*)dst, (const float*)src, (int64_t)n_tokens, H, ds, n);
+    else imp_launch(gather_head_cols_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)dst, (const __nv_bfloat16*)src, (int64_t)n_tokens, H, ds, n);
+    IMP_RETURN_LAUNCH();
+}

@@ -547,7 +547,7 @@ __global__ void __launch_bounds__(WARPS * 32, NR == 1 ? 4 : 2) attn_decode_kerne
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = imp_first_key(pos, window);
     const int first16 = first & ~15;
     const int total_steps = (pos - first16) / 16 + 1;
     // balanced ranges: every split gets floor or ceil of total / n_splits steps, none is left empty while others hold two
@@ -1061,7 +1061,7 @@ __global__ void __launch_bounds__((DT_CONSUMERS + 1) * 32) attn_decode_tma_kerne
         return;
     }
     const int* bt = block_table + (int64_t)seq * bt_stride;
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = imp_first_key(pos, window);
     const int first_al = first & ~(DT_KEYS - 1);
     const int total_stages = (pos - first_al) / DT_KEYS + 1;
     // balanced ranges: every split gets floor or ceil of total / n_splits stages
@@ -1578,15 +1578,15 @@ __global__ void __launch_bounds__(2 * HPC * 32) attn_prefill_kernel(
         const bool used = warp_used && rr < n_rows;
         const int pos = pos0 + rr;
         rows[r].limit = used ? pos : -1;
-        rows[r].first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        rows[r].first = imp_first_key(pos, window);
         qrow[r] = used ? q + (int64_t)(tok0 + rr) * q_stride + (int64_t)head * DH : nullptr;
     }
     if (warp_used) my_last = pos0 + min(n_rows, sub * 16 + 16) - 1;
-    const int my_first = (window > 0 && pos0 + sub * 16 - window + 1 > 0) ? pos0 + sub * 16 - window + 1 : 0;
+    const int my_first = imp_first_key(pos0 + sub * 16, window);
     const int my_lo_limit = pos0 + sub * 16;          // the smallest limit among the warp's rows
-    const int my_hi_first = (window > 0 && my_last - window + 1 > 0) ? my_last - window + 1 : 0;   // the largest first
+    const int my_hi_first = imp_first_key(my_last, window);   // the largest first
 
-    const int first_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int first_tile = imp_first_key(pos0, window);
     const int j_begin = first_tile & ~(PRE_KEYS - 1);
     const int n_stages = (pos_last - j_begin) / PRE_KEYS + 1;
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw);

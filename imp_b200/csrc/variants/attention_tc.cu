@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
         it.geometry_ok = it.seq >= 0 && it.seq < n_seqs && it.pos0 >= 0 && it.rows >= 1 && it.rows <= FA_BM &&
                          it.pos_last / P < bt_stride;
         // key tiles [kt_lo, kt_hi]: from the window's start of the first row to the last row's own key
-        it.first_key = (window > 0 && it.pos0 - window + 1 > 0) ? it.pos0 - window + 1 : 0;
+        it.first_key = imp_first_key(it.pos0, window);
         it.kt_lo = it.first_key / FA_BN;
         const int kt_hi = it.geometry_ok ? it.pos_last / FA_BN : it.kt_lo - 1;
         it.n_kt = kt_hi - it.kt_lo + 1;
@@ -480,9 +480,9 @@ __global__ void __launch_bounds__(FaCfg<NQ>::THREADS, 1) attn_prefill_tc_kernel(
             tc_fence_after_sync();
             if ((warp & 3) == 0 && lane == 0) FA_TR(1 + w, t_n * 6 + 1);
             // a tile needs the mask when a key of it lies behind the first row's position or before the last row's window
-            const bool masked = (k0 + FA_BN - 1 > pos0) || (window > 0 && pos0 + FA_BM - 1 - k0 >= window);
+            const bool masked = (k0 + FA_BN - 1 > pos0) || imp_first_key(pos0 + FA_BM - 1, window) > k0;
             const int hi = p - k0;                                        // columns <= hi are not in the future
-            const int lo = window > 0 ? p - window + 1 - k0 : -(1 << 30); // columns >= lo are inside the window
+            const int lo = window != 0 ? imp_first_key(p, window) - k0 : -(1 << 30); // columns >= lo are inside the window (or the query's chunk)
             // the whole row of S: four loads in flight, one wait
             uint32_t sr[FA_BN / 32][32];
 #pragma unroll
@@ -749,7 +749,7 @@ static int fa_prefill(void* out, int64_t out_stride, const void* q, int64_t q_st
                   "imp_attn_prefill_tc: page size %d or strides %lld / %lld not supported by this kernel", P,
                   (long long)q_stride, (long long)out_stride);
     IMP_CHECK_ARG(q_stride >= (int64_t)Hq * DH && out_stride >= (int64_t)Hq * DH && n_tokens > 0 && num_pages > 0 &&
-                      window >= 0 && scale > 0.f,
+                      scale > 0.f,
                   "imp_attn_prefill_tc: bad geometry");
     IMP_CHECK_ARG(((uintptr_t)q % 16) == 0 && ((uintptr_t)kc % 16) == 0 && ((uintptr_t)vc % 16) == 0 && ((uintptr_t)out % 16) == 0,
                   "imp_attn_prefill_tc: pointers must be 16-byte aligned");
