@@ -28,6 +28,7 @@ Other runs, each printing its own JSON line:
     python bench.py --workload 0.6b [--dtype float32]     64 requests, prompts 16..1024, 256 greedy tokens, 512-token portions
     python bench.py --arch kazedra [--layers N] [--batch B]    Kazedra beside Qwen3 at equal sizes: prefill and decode
     python bench.py --arch kuzipel [--layers N] [--batch B]    Kuzipel beside Kazedra and Qwen3 at equal sizes
+    python bench.py --arch pemidra [--layers N] [--batch B]    Pemidra beside Kazedra and Qwen3 at equal sizes
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
@@ -733,12 +734,32 @@ def kuzipel_config(width, heads, kv_heads, ff, layers, vocab):
             "max_positions": 8192}
 
 
+def pemidra_config(width, heads, kv_heads, ff, layers, vocab):
+    """Layers cycle through the pair (attention with heads of 128, half of each head rotated, chunks of 1,024 positions,
+    beside the delta rule with a decay per key channel, heads of 128 and four taps: Kazedra's geometry), retention (heads of
+    128 keys and 128 values) and the generalised delta rule (heads of 64); every layer has the dense feed-forward of the
+    models beside it, so that a token meets the same feed-forward weights."""
+    pair = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                     "rot": {"base": 10000.0, "dims": 64}},
+            "right": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    n_ret = width // 128
+    kinds = [("parallel", pair),
+             ("retention", {"heads": n_ret, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 4.0 * h / max(n_ret - 1, 1)) for h in range(n_ret)]}),
+             ("general_delta", {"heads": width // 64, "dim": 64, "decay_rank": 64})]
+    mlp = {"kind": "dense", "ff": ff}
+    lays = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Pemidra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 1.0, "layers": lays,
+            "max_positions": 8192}
+
+
 def run_arch(args):
-    """Prefill and decode of Kazedra or Kuzipel beside the models the engine already had at equal sizes (random weights): a
+    """Prefill and decode of Kazedra, Kuzipel or Pemidra beside the models the engine already had at equal sizes (random weights): a
     2,048-token prompt whole and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device
     time between CUDA events."""
     if args.arch == "kuzipel":
-        return run_arch_kuzipel(args)
+        return run_arch_beside(args, "kuzipel", kuzipel_config)
+    if args.arch == "pemidra":
+        return run_arch_beside(args, "pemidra", pemidra_config)
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
     if args.only in ("prefill", "decode"):
@@ -793,30 +814,31 @@ def run_arch(args):
     return 0
 
 
-def run_arch_kuzipel(args):
+def run_arch_beside(args, arch, config_of):
+    """`arch` (its configuration made by `config_of`) beside Kazedra and Qwen3 at equal width and inner size."""
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
     if args.only in ("prefill", "decode"):
         width, heads, kv, ff = ARCH_SHAPES[args.shape]
         rng = random.Random(0)
-        eng, _ = make_engine(kuzipel_config(width, heads, kv, ff, layers, vocab), args, B, 4096)
+        eng, _ = make_engine(config_of(width, heads, kv, ff, layers, vocab), args, B, 4096)
         if args.only == "prefill":
             ms = time_prefill(eng, rng, vocab, args.tokens or 2048, args.chunk, reps=max(1, args.steps))
-            print(json.dumps({"arch": "kuzipel", "only": "prefill", "shape": args.shape, "layers": layers, "tokens": args.tokens or 2048,
+            print(json.dumps({"arch": arch, "only": "prefill", "shape": args.shape, "layers": layers, "tokens": args.tokens or 2048,
                               "chunk": args.chunk, "ms": spread(ms)}))
         else:
             reqs = start_decoding(eng, rng, vocab, B, args.context or 2048, args.steps + args.warmup + 16)
             for _ in range(args.warmup):
                 eng.step()
             ms = timed_steps(eng, args.steps, B) / args.steps
-            print(json.dumps({"arch": "kuzipel", "only": "decode", "shape": args.shape, "layers": layers, "batch": B,
+            print(json.dumps({"arch": arch, "only": "decode", "shape": args.shape, "layers": layers, "batch": B,
                               "context": args.context or 2048, "ms_per_step": round(ms, 4)}))
             stop(eng, reqs)
         return 0
-    out = {"arch": "kuzipel", "beside": ["kazedra", "qwen3"], "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
+    out = {"arch": arch, "beside": ["kazedra", "qwen3"], "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
     with ClockSampler() as clocks:
         for name, (width, heads, kv, ff) in ARCH_SHAPES.items():
-            models = {"kuzipel": kuzipel_config(width, heads, kv, ff, layers, vocab),
+            models = {arch: config_of(width, heads, kv, ff, layers, vocab),
                       "kazedra": kazedra_config(width, heads, kv, ff, layers, vocab),
                       "qwen3": dict(MODEL, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
                                     intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)}
@@ -840,8 +862,8 @@ def run_arch_kuzipel(args):
                               "graph_replays": info["graph_replays"] - before["graph_replays"], "fallback_calls": info["fallback_calls"]}
                 del eng
             for other in ("kazedra", "qwen3"):
-                row["prefill_ratio_to_" + other] = round(row["kuzipel"]["prefill_2048_ms"]["median"] / row[other]["prefill_2048_ms"]["median"], 3)
-                row["decode_ratio_to_" + other] = round(row["kuzipel"]["decode_ms_per_step"] / row[other]["decode_ms_per_step"], 3)
+                row["prefill_ratio_to_" + other] = round(row[arch]["prefill_2048_ms"]["median"] / row[other]["prefill_2048_ms"]["median"], 3)
+                row["decode_ratio_to_" + other] = round(row[arch]["decode_ms_per_step"] / row[other]["decode_ms_per_step"], 3)
             out["shapes"][name] = row
     out["clocks"] = clocks.summary()
     print(json.dumps(out))
@@ -880,7 +902,7 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
-    ap.add_argument("--arch", default="", choices=["", "kazedra", "kuzipel"],
+    ap.add_argument("--arch", default="", choices=["", "kazedra", "kuzipel", "pemidra"],
                     help="prefill and decode of this architecture beside the Qwen3 decoder at equal sizes (not the default workload)")
     ap.add_argument("--shape", default="8b", choices=["1b", "8b"], help="with --arch and --only: which of the shapes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
