@@ -51,12 +51,13 @@ template <int N> __device__ __forceinline__ void gs_wait_group() {
 
 // SWIGLU: the 16 rows of a CTA are 8 gate rows followed by their 8 up rows (the caller interleaves
 // the two matrices in blocks of 8 rows), so accumulator slots c and c+2 of a lane hold gate and up
-// of the same output column and token; the epilogue writes silu(gate) * up into C[M, N/2].
+// of the same output column and token; the epilogue writes act(gate) * up into C[M, N/2] (gate_act: 0 silu, 1 the tanh
+// form of gelu).
 template <int NT, typename TO, bool SWIGLU, int STAGES, int RG>
 __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __restrict__ C, int64_t ldc,
                                                                     const __nv_bfloat16* __restrict__ A, int64_t lda,
                                                                     const __nv_bfloat16* __restrict__ W, int64_t ldw,
-                                                                    int M, int N, int K) {
+                                                                    int M, int N, int K, int gate_act) {
     IMP_TL_BEGIN(5)
     extern __shared__ __align__(128) unsigned char gs_smem[];
     constexpr int STAGE_BYTES = gs_stage_bytes(NT, RG);
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __r
                 const int col = (c_tile * RG + rg) * 8 + (l >> 2);
                 const int tok = 8 * nt + 2 * (l & 3) + c;
                 if (n0 + (l >> 2) + 8 < N && tok < M)
-                    C[(int64_t)tok * ldc + col] = from_float<TO>(gate / (1.f + expf(-gate)) * up);
+                    C[(int64_t)tok * ldc + col] = from_float<TO>(gate_act_f(gate, gate_act) * up);
             }
         } else {
             // 16 rows x 8*NT tokens = NT*128 sums; thread i takes register slot i / 32 of lane i % 32.
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32 * RG) gemm_stream_kernel(TO* __r
 
 template <int NT, typename TO, bool SWIGLU, int STAGES, int RG>
 static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
-                                    int64_t ldw, int M, int N, int K, cudaStream_t s) {
+                                    int64_t ldw, int M, int N, int K, cudaStream_t s, int gate_act = 0) {
     static bool attr_set = false;   // once per instantiation (one device per process)
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, TO, SWIGLU, STAGES, RG>,
@@ -215,7 +216,7 @@ static cudaError_t launch_stream_st(TO* C, int64_t ldc, const __nv_bfloat16* A, 
     // (the kernel itself takes any grid size: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...).
     const int grid = n_tiles;
     return imp_launch(gemm_stream_kernel<NT, TO, SWIGLU, STAGES, RG>, dim3(grid), dim3(GS_WARPS * 32 * RG), gs_smem_bytes(NT, STAGES, RG), s, C, ldc,
-                      A, lda, W, ldw, M, N, K);
+                      A, lda, W, ldw, M, N, K, gate_act);
 }
 
 // Ring depth.  Five stages let three CTAs share an SM (444 resident CTAs on a B200's 148 SMs).  A product with
@@ -233,7 +234,7 @@ static int gs_env_stages() {
 
 template <int NT, typename TO, bool SWIGLU>
 static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W,
-                                    int64_t ldw, int M, int N, int K, cudaStream_t s) {
+                                    int64_t ldw, int M, int N, int K, cudaStream_t s, int gate_act = 0) {
     int stages = gs_env_stages();
     // Up to 8 tokens: two row groups per CTA where 32-row tiles still give about one CTA per SM or more.
     // With at least one such tile per SM, four stages of 21 KiB (two CTAs per SM); with 96/148 of that
@@ -244,23 +245,23 @@ static cudaError_t launch_stream_nt(TO* C, int64_t ldc, const __nv_bfloat16* A, 
     // (With one or two tokens the activations are a small share of the traffic and more, smaller CTAs win.)
     const int sms = imp_sm_count();
     if (NT == 1 && M >= 3 && rg_env >= 2 && stages == 0 && (N + 31) / 32 >= sms)
-        return launch_stream_st<1, TO, SWIGLU, 4, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        return launch_stream_st<1, TO, SWIGLU, 4, 2>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
     if (NT == 1 && M >= 3 && rg_env == 3 && stages == 0 && (N + 31) / 32 >= (sms * 96 + 147) / 148 && (N + 31) / 32 < sms)
-        return launch_stream_st<1, TO, SWIGLU, 6, 2>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        return launch_stream_st<1, TO, SWIGLU, 6, 2>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
     if (stages == 0) stages = (NT == 1 && (N + 15) / 16 <= 2 * sms) ? 8 : 5;
     switch (stages) {
-        case 4: return launch_stream_st<NT, TO, SWIGLU, 4, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        case 6: return launch_stream_st<NT, TO, SWIGLU, 6, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        case 8: return launch_stream_st<NT, TO, SWIGLU, 8, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
-        default: return launch_stream_st<NT, TO, SWIGLU, 5, 1>(C, ldc, A, lda, W, ldw, M, N, K, s);
+        case 4: return launch_stream_st<NT, TO, SWIGLU, 4, 1>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
+        case 6: return launch_stream_st<NT, TO, SWIGLU, 6, 1>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
+        case 8: return launch_stream_st<NT, TO, SWIGLU, 8, 1>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
+        default: return launch_stream_st<NT, TO, SWIGLU, 5, 1>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
     }
 }
 
 template <typename TO, bool SWIGLU>
 static int launch_stream(TO* C, int64_t ldc, const __nv_bfloat16* A, int64_t lda, const __nv_bfloat16* W, int64_t ldw,
-                         int M, int N, int K, cudaStream_t s) {
-    const cudaError_t e = (M <= 8) ? launch_stream_nt<1, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s)
-                                   : launch_stream_nt<2, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s);
+                         int M, int N, int K, cudaStream_t s, int gate_act = 0) {
+    const cudaError_t e = (M <= 8) ? launch_stream_nt<1, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act)
+                                   : launch_stream_nt<2, TO, SWIGLU>(C, ldc, A, lda, W, ldw, M, N, K, s, gate_act);
     if (e != cudaSuccess) {
         imp_set_error("gemm_stream: %s", cudaGetErrorString(e));
         return (int)e;
@@ -287,14 +288,21 @@ IMP_API int imp_gemm_bf16_stream(void* C, int64_t ldc, int out_dtype, const void
 
 // C[M, N/2] = silu(gate) * up where W[N, K] holds gate and up rows interleaved in blocks of 8
 // (rows 16j..16j+7 = gate rows 8j..8j+7, rows 16j+8..16j+15 = up rows 8j..8j+7); bfloat16 output.
-IMP_API int imp_gemm_bf16_stream_swiglu(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw,
-                                        int M, int N, int K, void* stream) {
+// imp_gemm_bf16_stream_gated: the same with the gate's activation chosen (0 silu, 1 the tanh form of gelu).
+IMP_API int imp_gemm_bf16_stream_gated(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                       int M, int N, int K, int act, void* stream) {
     if (M == 0 || N == 0) return 0;
+    IMP_CHECK_ARG(act == 0 || act == 1, "imp_gemm_bf16_stream_gated: unknown activation %d", act);
     IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_stream_swiglu: bad argument");
     IMP_CHECK_ARG(M <= 16, "imp_gemm_bf16_stream_swiglu: M %d exceeds 16", M);
     IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_stream_swiglu: %d interleaved rows are not a multiple of 16", N);
     IMP_CHECK_ARG(ldc >= N / 2 && lda >= K && ldw >= K, "imp_gemm_bf16_stream_swiglu: leading dimension too small");
     if (K % 8 || lda % 8 || ldw % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16) return IMP_ERR_UNSUPPORTED;
     return launch_stream<__nv_bfloat16, true>((__nv_bfloat16*)C, ldc, (const __nv_bfloat16*)A, lda,
-                                              (const __nv_bfloat16*)W, ldw, M, N, K, (cudaStream_t)stream);
+                                              (const __nv_bfloat16*)W, ldw, M, N, K, (cudaStream_t)stream, act);
+}
+
+IMP_API int imp_gemm_bf16_stream_swiglu(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw,
+                                        int M, int N, int K, void* stream) {
+    return imp_gemm_bf16_stream_gated(C, ldc, A, lda, W, ldw, M, N, K, 0, stream);
 }

@@ -34,12 +34,13 @@ constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int TC_TMEM_COLS = 256;
 
-enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU_BF16 = 2, TC_OUT_QKV_ROPE = 3 };
+// TC_OUT_GEGLU_BF16 is a value of the entry points only: the gated epilogue with the other activation (a kernel parameter).
+enum TcEpilogue : int { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU_BF16 = 2, TC_OUT_QKV_ROPE = 3, TC_OUT_GEGLU_BF16 = 4 };
 
 // Store 32 consecutive accumulator columns of one row (converted as the epilogue asks).
 template <int EPI>
 __device__ __forceinline__ void tc_store32(void* __restrict__ Cv, int64_t ldc, int row, int col0, int M, int N,
-                                           const float (&v)[32]) {
+                                           const float (&v)[32], int gate_act = 0) {
     if (row >= M || col0 >= N) return;
     if (EPI == TC_OUT_F32) {
         float* dst = reinterpret_cast<float*>(Cv) + (int64_t)row * ldc + col0;
@@ -76,7 +77,7 @@ __device__ __forceinline__ void tc_store32(void* __restrict__ Cv, int64_t ldc, i
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float gate = v[16 * j + i], up = v[16 * j + 8 + i];
-                o[8 * j + i] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+                o[8 * j + i] = __float2bfloat16_rn(gate_act_f(gate, gate_act) * up);
             }
         if (col0 + 32 <= N && (ldc % 8) == 0) {
             reinterpret_cast<uint4*>(dst)[0] = *reinterpret_cast<uint4*>(&o[0]);
@@ -91,7 +92,7 @@ __device__ __forceinline__ void tc_store32(void* __restrict__ Cv, int64_t ldc, i
 template <int EPI>
 __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_w, void* __restrict__ Cv,
-                                                         int64_t ldc, int M, int N, int K, int* status) {
+                                                         int64_t ldc, int M, int N, int K, int* status, int gate_act) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ unsigned char tc_smem_raw[];
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         for (int c = 0; c < TC_BN / 32; ++c) {
             float v[32];
             tc_ld32(lane_base + (uint32_t)(c * 32), v);
-            tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+            tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v, gate_act);
         }
     }
     tc_fence_before_sync();
@@ -200,7 +201,7 @@ template <int EPI>
 __global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_w,
                                                                             void* __restrict__ Cv, int64_t ldc, int M, int N,
-                                                                            int K, int* status) {
+                                                                            int K, int* status, int gate_act) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ unsigned char tc_smem_raw[];
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(TCP_THREADS, 1) gemm_tc_persistent_kernel(cons
             for (int c = 0; c < TC_BN / 32; ++c) {
                 float v[32];
                 tc_ld32(taddr + (uint32_t)(c * 32), v);
-                tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v);
+                tc_store32<EPI>(Cv, ldc, row, n0 + c * 32, M, N, v, gate_act);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -578,7 +579,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         void* __restrict__ Cv, int64_t ldc, int M, int N, int K, int* status,
                         const __grid_constant__ QkvRopeArgs qkv, int splits, int kb_per_split, int64_t split_stride,
-                        const __grid_constant__ CUtensorMap map_c, int tma_store) {
+                        const __grid_constant__ CUtensorMap map_c, int tma_store, int gate_act) {
     // tma_store (bfloat16 and SwiGLU epilogues): C goes out through shared memory and TMA stores described by map_c
     // (boxes of 128 rows x 64 columns, clipped at the matrix edges) instead of 16-byte stores from every thread.
     // splits > 1 (32-bit output only): the K range is cut into `splits` parts, each (tile, part) is a unit of work of its
@@ -750,7 +751,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) {
                                     const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
-                                    o[8 * h + i] = gate / (1.f + expf(-gate)) * up;
+                                    o[8 * h + i] = gate_act_f(gate, gate_act) * up;
                                 }
                             q[2 * cc] = tc2_pack8(o);
                             q[2 * cc + 1] = tc2_pack8(o + 8);
@@ -771,7 +772,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS, 1)
                 for (int c = 0; c < TC2_BN / 32; ++c) {
                     float v[32];
                     tc_ld32(taddr + (uint32_t)(c * 32), v);
-                    tc_store32<EPI == TC_OUT_QKV_ROPE ? TC_OUT_BF16 : EPI>(Cz, ldc, row, n0 + c * 32, M, N, v);
+                    tc_store32<EPI == TC_OUT_QKV_ROPE ? TC_OUT_BF16 : EPI>(Cz, ldc, row, n0 + c * 32, M, N, v, gate_act);
                 }
             }
             tc_fence_before_sync();
@@ -840,7 +841,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
                                                               const __grid_constant__ CUtensorMap map_x, void* __restrict__ Cv,
                                                               int64_t ldc, int64_t split_stride, int M, int N, int K,
                                                               int kb_per_split, int tile_rows, int* status,
-                                                              uint32_t wait_limit, int skip_kb) {
+                                                              uint32_t wait_limit, int skip_kb, int gate_act) {
     constexpr int TCS_STAGES = tcs_rows_stages<BN, WROWS>();
     static_assert(tcs_rows_stage_bytes<BN, WROWS>() >= TCS_W_BYTES && tcs_rows_stage_bytes<BN, WROWS>() % 1024 == 0, "a stage spans what the MMA reads");
     IMP_TL_BEGIN(10 + EPI)
@@ -956,7 +957,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_swap_kernel(const __grid_const
                     const float up = __shfl_xor_sync(0xffffffffu, v[i], 8);   // lane r + 8 holds the matching up row
                     const int tok = c * 32 + i;
                     if (is_gate && tok < M && col + 8 < N && r < tile_rows)
-                        base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
+                        base[(int64_t)tok * ldc + ocol] = __float2bfloat16_rn(gate_act_f(v[i], gate_act) * up);
                 }
             } else if (col < N && r < tile_rows) {
                 if (EPI == TC_OUT_F32) {
@@ -1068,7 +1069,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int64_t
 
 template <int EPI>
 static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw128, int M,
-                     int N, int K, int* status, cudaStream_t s) {
+                     int N, int K, int* status, cudaStream_t s, int gate_act = 0) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
@@ -1105,17 +1106,17 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
         if (EPI != TC_OUT_F32 && tma_out && ldc % 8 == 0)
             tma_store = make_map(&mc, C, M, EPI == TC_OUT_SWIGLU_BF16 ? N / 2 : N, ldc, 128) == 0 ? 1 : 0;
         cudaError_t e = imp_launch(gemm_tc_pair_kernel<EPI>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES, s, ma, mw128,
-                                   C, ldc, M, N, K, status, QkvRopeArgs{}, 1, (K + TC_BK - 1) / TC_BK, (int64_t)0, mc, tma_store);
+                                   C, ldc, M, N, K, status, QkvRopeArgs{}, 1, (K + TC_BK - 1) / TC_BK, (int64_t)0, mc, tma_store, gate_act);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
         return 0;
     }
     const int num_m = (M + TC_BM - 1) / TC_BM, num_n = (N + TC_BN - 1) / TC_BN;
     if (mode == 1) {
-        gemm_tc_kernel<EPI><<<dim3(num_m, num_n), 128, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status);
+        gemm_tc_kernel<EPI><<<dim3(num_m, num_n), 128, TC_SMEM_BYTES, s>>>(ma, mw, C, ldc, M, N, K, status, gate_act);
     } else {
         const int total = num_m * num_n;
         cudaError_t e = imp_launch(gemm_tc_persistent_kernel<EPI>, dim3(total < sms ? total : sms), dim3(TCP_THREADS),
-                                   (size_t)TC_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, status);
+                                   (size_t)TC_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, status, gate_act);
         if (e != cudaSuccess) { imp_set_error("gemm_tc: %s", cudaGetErrorString(e)); return (int)e; }
         return 0;
     }
@@ -1123,13 +1124,15 @@ static int launch_tc(void* C, int64_t ldc, const CUtensorMap& ma, const CUtensor
 }
 
 // epilogue: 0 = bfloat16 C[M,N]; 1 = float32 C[M,N]; 2 = bfloat16 C[M,N/2] = silu(gate) * up with
-// gate and up rows of W interleaved in runs of 8.
+// gate and up rows of W interleaved in runs of 8; 4 = the same with the tanh form of gelu on the gate.
 // Returns IMP_ERR_UNSUPPORTED when the operands do not meet the alignment rules of the tensor copies
 // (bases on 16-byte boundaries, row strides multiples of 8 elements): the caller uses another kernel.
 IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, int64_t lda, const void* W, int64_t ldw,
                              int M, int N, int K, int* status, void* stream) {
     if (M == 0 || N == 0) return 0;
     IMP_CHECK_ARG(C && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_tc: bad argument");
+    const int gate_act = epilogue == TC_OUT_GEGLU_BF16 ? 1 : 0;
+    if (gate_act) epilogue = TC_OUT_SWIGLU_BF16;
     IMP_CHECK_ARG(epilogue >= 0 && epilogue <= 2, "imp_gemm_bf16_tc: unknown epilogue %d", epilogue);
     IMP_CHECK_ARG(lda >= K && ldw >= K && ldc >= (epilogue == 2 ? N / 2 : N), "imp_gemm_bf16_tc: leading dimension too small");
     if (epilogue == 2) IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_tc: %d interleaved rows are not a multiple of 16", N);
@@ -1142,7 +1145,7 @@ IMP_API int imp_gemm_bf16_tc(void* C, int64_t ldc, int epilogue, const void* A, 
     if (int rc = make_map(&mw128, W, N, K, ldw, 128)) return rc;
     if (epilogue == TC_OUT_BF16) return launch_tc<TC_OUT_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
     if (epilogue == TC_OUT_F32) return launch_tc<TC_OUT_F32>(C, ldc, ma, mw, mw128, M, N, K, status, s);
-    return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s);
+    return launch_tc<TC_OUT_SWIGLU_BF16>(C, ldc, ma, mw, mw128, M, N, K, status, s, gate_act);
 }
 
 // ---- many rows, few tiles: the K range in parts ------------------------------------------------------
@@ -1195,7 +1198,7 @@ IMP_API int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda
     const int pairs = units < sms / 2 ? units : sms / 2;
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_F32>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)scratch, (int64_t)N, M, N, K, status, QkvRopeArgs{}, splits,
-                               kb_per_split, (int64_t)M * N, CUtensorMap{}, 0);
+                               kb_per_split, (int64_t)M * N, CUtensorMap{}, 0, 0);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_partials: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1231,7 +1234,7 @@ static int tcs_tile_rows(int M, int N, int splits) {
 }
 
 static int tcs_splits(int M, int N, int K, int epilogue) {
-    if (epilogue == TC_OUT_SWIGLU_BF16) return 1;
+    if (epilogue == TC_OUT_SWIGLU_BF16 || epilogue == TC_OUT_GEGLU_BF16) return 1;
     const int slots = tcs_slots(M);                      // resident CTAs
     const int tiles = (N + 127) / 128;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
@@ -1249,7 +1252,7 @@ IMP_API int64_t imp_gemm_bf16_tc_swap_scratch_floats(int M, int N, int K, int ep
 
 template <int BN, int EPI, int WROWS = 128>
 static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensorMap& mw, const CUtensorMap& mx, int M, int N,
-                      int K, int splits, int kb_per_split, int tile_rows, int* status, cudaStream_t s) {
+                      int K, int splits, int kb_per_split, int tile_rows, int* status, cudaStream_t s, int gate_act = 0) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_swap_kernel<BN, EPI, WROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1259,7 +1262,7 @@ static int launch_tcs(void* C, int64_t ldc, int64_t split_stride, const CUtensor
     }
     dim3 grid((N + tile_rows - 1) / tile_rows, 1, splits);
     cudaError_t e = imp_launch(gemm_tc_swap_kernel<BN, EPI, WROWS>, grid, dim3(128), (size_t)tcs_rows_smem_bytes<BN, WROWS>(), s, mw, mx,
-                               C, ldc, split_stride, M, N, K, kb_per_split, tile_rows, status, g_tcs_wait_limit, g_tcs_skip_kb);
+                               C, ldc, split_stride, M, N, K, kb_per_split, tile_rows, status, g_tcs_wait_limit, g_tcs_skip_kb, gate_act);
     if (e != cudaSuccess) { imp_set_error("gemm_tc_swap: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1271,6 +1274,8 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
     if (M == 0 || N == 0) return 0;
     IMP_CHECK_ARG((C || partials_only) && A && W && M > 0 && N > 0 && K > 0, "imp_gemm_bf16_tc_swap: bad argument");
     IMP_CHECK_ARG(M <= 128, "imp_gemm_bf16_tc_swap: M %d exceeds 128", M);
+    const int gate_act = epilogue == TC_OUT_GEGLU_BF16 ? 1 : 0;
+    if (gate_act) epilogue = TC_OUT_SWIGLU_BF16;
     IMP_CHECK_ARG(epilogue >= 0 && epilogue <= 2, "imp_gemm_bf16_tc_swap: unknown epilogue %d", epilogue);
     if (epilogue == 2) IMP_CHECK_ARG(N % 16 == 0, "imp_gemm_bf16_tc_swap: %d interleaved rows are not a multiple of 16", N);
     IMP_CHECK_ARG(lda >= K && ldw >= K && ldc >= (epilogue == 2 ? N / 2 : N), "imp_gemm_bf16_tc_swap: leading dimension too small");
@@ -1320,12 +1325,12 @@ static int gemm_bf16_tc_swap_impl(void* C, int64_t ldc, int epilogue, const void
         // gate/up of the 8B shape (256 tiles of 96 rows): 42.3 -> 40.5 us at 64 tokens with five stages instead of four,
         // 34.8 -> 34.7 at 8 tokens with six instead of five; whole steps 0.2 to 0.5 % faster
         rc = (BN == 64 && tile_rows == 96 && (rows96 & 1))
-                 ? launch_tcs<64, TC_OUT_SWIGLU_BF16, 96>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
+                 ? launch_tcs<64, TC_OUT_SWIGLU_BF16, 96>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s, gate_act)
            : (BN == 32 && tile_rows == 96 && (rows96 & 2))
-                 ? launch_tcs<32, TC_OUT_SWIGLU_BF16, 96>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-           : BN == 32 ? launch_tcs<32, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-           : BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s)
-                      : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s);
+                 ? launch_tcs<32, TC_OUT_SWIGLU_BF16, 96>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s, gate_act)
+           : BN == 32 ? launch_tcs<32, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s, gate_act)
+           : BN == 64 ? launch_tcs<64, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s, gate_act)
+                      : launch_tcs<128, TC_OUT_SWIGLU_BF16>(C, ldc, 0, mw, mx, M, N, K, 1, kb_per_split, tile_rows, status, s, gate_act);
     }
     if (rc) return rc;
     IMP_RETURN_LAUNCH();
@@ -1448,7 +1453,7 @@ IMP_API int imp_gemm_bf16_tc_qkv_rope(const void* A, int64_t lda, const void* W,
     }
     cudaError_t e = imp_launch(gemm_tc_pair_kernel<TC_OUT_QKV_ROPE>, dim3(2 * pairs), dim3(TCP_THREADS), (size_t)TC2_SMEM_BYTES,
                                (cudaStream_t)stream, ma, mw128, (void*)nullptr, (int64_t)0, M, N, K, status, a, 1,
-                               (K + TC_BK - 1) / TC_BK, (int64_t)0, mq, q_tma);
+                               (K + TC_BK - 1) / TC_BK, (int64_t)0, mq, q_tma, 0);
     if (e != cudaSuccess) { imp_set_error("imp_gemm_bf16_tc_qkv_rope: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }

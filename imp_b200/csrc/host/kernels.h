@@ -73,6 +73,8 @@ int imp_gemm_bf16_stream(void* C, int64_t ldc, int out_dtype, const void* A, int
                          int N, int K, void* stream);
 int imp_gemm_bf16_stream_swiglu(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N,
                                 int K, void* stream);
+int imp_gemm_bf16_stream_gated(void* C, int64_t ldc, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N,
+                               int K, int act, void* stream);
 int imp_gemm_bf16_tc_splits(int M, int N, int K);
 int imp_gemm_bf16_tc_partials(float* scratch, const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K, int* status,
                               void* stream);
@@ -176,4 +178,4 @@ int imp_moe_combine(void* out, const void* y, const int* pair_row, const float* 
 }
 
 // Epilogues of the tcgen05 products.
-enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU = 2 };
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_SWIGLU = 2, TC_OUT_GEGLU = 4 };   // 2 / 4: act(gate) * up, act silu / gelu (tanh form)

@@ -106,7 +106,7 @@ static void gemm_stream(Runtime& rt, Tensor out, const Tensor& a, const Tensor& 
 
 static bool gemm_tc(Runtime& rt, Tensor out, const Tensor& a, const Tensor& w, int epilogue = -1) {
     if (epilogue < 0) epilogue = out.dtype == F32 ? TC_OUT_F32 : TC_OUT_BF16;
-    if (epilogue != TC_OUT_SWIGLU) {
+    if (epilogue != TC_OUT_SWIGLU && epilogue != TC_OUT_GEGLU) {
         // few 256 x 256 tiles for the device's CTA pairs (a portion of a prompt): the K range in parts, then their sum
         const int M = (int)rows(a), N = (int)rows(w), K = (int)cols(a);
         const int n_splits = imp_gemm_bf16_tc_splits(M, N, K);
@@ -230,38 +230,33 @@ Branch linear(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w, bool ma
     return Branch::of(out);
 }
 
-void linear_swiglu(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w) {
+void linear_gated(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w, int act) {
     const int64_t M = M_of(x), F = cols(out);
     if (M == 0) return;
+    need(act == 0 || act == 1, "linear_gated: unknown activation");
+    const int epi = act == 0 ? TC_OUT_SWIGLU : TC_OUT_GEGLU;
     const bool bf16 = x.dtype == BF16 && w.dtype == BF16 && out.dtype == BF16;
     const bool lib = use_library_gemm();
-    if (bf16 && M > stream_m_max() && M <= SMALL_M_MAX && !lib && gemm_tc_swap(rt, out, x, w, TC_OUT_SWIGLU)) return;
+    if (bf16 && M > stream_m_max() && M <= SMALL_M_MAX && !lib && gemm_tc_swap(rt, out, x, w, epi)) return;
     if (bf16 && M <= SMALL_M_MAX) {
-        const int rc = imp_gemm_bf16_stream_swiglu(out.data, out.stride0, x.data, x.stride0, w.data, w.stride0, (int)M, (int)(2 * F),
-                                                   (int)cols(x), rt.stream);
+        const int rc = imp_gemm_bf16_stream_gated(out.data, out.stride0, x.data, x.stride0, w.data, w.stride0, (int)M, (int)(2 * F),
+                                                  (int)cols(x), act, rt.stream);
         if (rc != -2) {
             ++rt.launches;
-            check_launch(rc, "gemm_bf16_stream_swiglu");
+            check_launch(rc, "gemm_bf16_stream_gated");
             return;
         }
     }
     if (bf16 && !lib) {
-        if (M <= TC_SWAP_MAX_M && gemm_tc_swap(rt, out, x, w, TC_OUT_SWIGLU)) return;
-        if (gemm_tc(rt, out, x, w, TC_OUT_SWIGLU)) return;
+        if (M <= TC_SWAP_MAX_M && gemm_tc_swap(rt, out, x, w, epi)) return;
+        if (gemm_tc(rt, out, x, w, epi)) return;
     }
-    Tensor gu = rt.empty(M, 2 * F, x.dtype);
-    linear(rt, gu, x, w);
-    swiglu(rt, out, gu, SWIGLU_INTERLEAVE);
-}
-
-void linear_gated(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w, int act) {
-    if (act == 0) return linear_swiglu(rt, out, x, w);
-    const int64_t M = M_of(x), F = cols(out);
-    if (M == 0) return;
     Tensor gu = rt.empty(M, 2 * F, x.dtype);
     linear(rt, gu, x, w);
     gated_act(rt, out, gu, SWIGLU_INTERLEAVE, act);
 }
+
+void linear_swiglu(Runtime& rt, Tensor out, const Tensor& x, const Tensor& w) { linear_gated(rt, out, x, w, 0); }
 
 // ---------------------------------------------------------------------------------------- norm
 void add_rmsnorm(Runtime& rt, Tensor h, const Branch& branch, const Tensor& weight, Tensor out, float eps, float offset,

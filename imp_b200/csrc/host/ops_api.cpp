@@ -74,6 +74,18 @@ IMP_EXPORT int imp_op_linear_swiglu(const ImpTensor* out, const ImpTensor* x, co
     });
 }
 
+// The same with the gate's activation chosen: 0 silu, 1 the tanh form of gelu.
+IMP_EXPORT int imp_op_linear_gated(const ImpTensor* out, const ImpTensor* x, const ImpTensor* w_interleaved, int act, void* stream,
+                                   int32_t* status) {
+    return guarded([&] {
+        if (!out || !x || !w_interleaved) fail(IMP_ERROR_INVALID_ARG, "imp_op_linear_gated: null tensor");
+        Runtime rt = runtime_for(stream, status);
+        rt.dtype = x->dtype;
+        linear_gated(rt, *out, *x, *w_interleaved, act);
+        g_fallbacks += rt.fallback_calls;
+    });
+}
+
 // h (+= branch); out = rmsnorm(h) * (weight + offset).  `branch` may be null; with parts != NULL the branch
 // is the unsummed product imp_op_linear left (branch then names where its sum belongs).
 IMP_EXPORT int imp_op_add_rmsnorm(const ImpTensor* h, const ImpTensor* branch, const float* parts, int n_splits,

@@ -145,10 +145,6 @@ __global__ void __launch_bounds__(256) rms_pair_mean_kernel(TA* __restrict__ out
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<TA>(fmaf(to_float(ar[i]) * ra, wa[i], to_float(br[i]) * rb * wb[i]));
 }
 
-__device__ __forceinline__ float gelu_tanh_f(float z) {
-    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
-
 // out[t, f] = act(gate) * up over rows [gate | up] (block == 0) or runs of `block` gate entries followed by their up entries.
 // act: 0 silu, 1 gelu (tanh form).
 template <typename T>
@@ -163,7 +159,7 @@ __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, 
         const int ui = block ? gi + block : F + f;
         const float g = to_float(gu[t * 2 * F + gi]);
         const float u = to_float(gu[t * 2 * F + ui]);
-        const float a = act == 0 ? g / (1.f + expf(-g)) : gelu_tanh_f(g);
+        const float a = gate_act_f(g, act);
         out[i] = from_float<T>(a * u);
     }
 }

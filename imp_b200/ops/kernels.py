@@ -114,6 +114,18 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tenso
     return out
 
 
+def linear_gated(out: torch.Tensor, x: torch.Tensor, w_interleaved: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """out[M, F] = act(x Wg^T) * (x Wu^T), act "silu" or "gelu_tanh", with the activation in the product's epilogue
+    where the library has such a kernel for the shape (csrc/host/linear.cpp `linear_gated`)."""
+    _need_cuda(out, x, w_interleaved)
+    if x.shape[0] == 0:
+        return out
+    act = {"silu": 0, "gelu_tanh": 1}[activation]
+    o, a, w = _view(out), _view(x), _view(w_interleaved)
+    _op_check(L.load().imp_op_linear_gated(ctypes.byref(o), ctypes.byref(a), ctypes.byref(w), act, _stream(), None), "linear_gated")
+    return out
+
+
 def cast(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     _need_cuda(dst, src)
     assert dst.numel() == src.numel() and dst.is_contiguous() and src.is_contiguous()

@@ -83,6 +83,7 @@ _SIGNATURES.update({
     "imp_op_fallback_calls": (c_int64, []),
     "imp_op_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "imp_op_linear_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "imp_op_linear_gated": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "imp_op_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                    c_int, c_void_p]),
     "imp_op_decode_splits": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),

@@ -206,6 +206,25 @@ def test_linear_swiglu_fused(K, M, F, K_):
     close(out, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
 
 
+@pytest.mark.parametrize("M", [1, 5, 11, 16, 40, 100, 130, 300, 1100])
+@pytest.mark.parametrize("F,K_", [(8, 64), (200, 96), (1536, 512), (24, 100)])
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_linear_gated_fused(K, M, F, K_, activation):
+    """The gated product with either activation, over the row counts that choose each of its kernels."""
+    x = rnd(M, K_, dtype=torch.bfloat16, seed=33).to(DEV)
+    wg = rnd(F, K_, dtype=torch.bfloat16, seed=34, scale=0.3).to(DEV)
+    wu = rnd(F, K_, dtype=torch.bfloat16, seed=35, scale=0.3).to(DEV)
+    w = K.interleave_gate_up(wg, wu)
+    out = K.linear_gated(torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV), x, w, activation)
+    g = x.double().cpu() @ wg.double().cpu().T
+    u = x.double().cpu() @ wu.double().cpu().T
+    if activation == "silu":
+        a = g / (1 + torch.exp(-g))
+    else:
+        a = 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    close(out, a * u, torch.bfloat16)
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (1, 8, 8), (130, 264, 72), (300, 520, 200), (257, 1000, 4104),
                                     (2048, 512, 1024)])
 @pytest.mark.parametrize("odtype", [torch.bfloat16, torch.float32])
