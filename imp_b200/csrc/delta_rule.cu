@@ -17,6 +17,8 @@
 // Every column of S evolves independently of the others, which is what the scan kernel's split rests on.
 // A token's result depends on the tokens before it only through S and the convolution's inputs, and the
 // order of every sum is fixed by the sizes alone: cutting a prompt into portions changes no bit.
+#include <algorithm>
+
 #include "common.cuh"
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
@@ -770,8 +772,11 @@ __global__ void __launch_bounds__(GP_BLOCK) gdelta_prepare_kernel(const TA* __re
 // unit vectors, q times D^(-1/2); dpre [T, H*D] float32 is the decay's pre-activation without dt_bias:
 //   g = exp(-exp(a_log[h]) * softplus(dpre + dt_bias));  beta = sigmoid(.)
 // Outputs per value head (reading key head h / (H / G)): kw = k, q, w = g, v, scal = (beta q . k, beta).
+// A CTA per (token, key head): its warps make the key head's q and k channels once, together, and then take the value
+// heads of that key head in turn (a warp per value head, up to GC_MAX_WARPS at a time).
+constexpr int GC_MAX_WARPS = 8;
 template <typename TA, int TAPS>
-__global__ void __launch_bounds__(GP_BLOCK) gdrc_prepare_kernel(
+__global__ void __launch_bounds__(GC_MAX_WARPS * 32) gdrc_prepare_kernel(
     const TA* __restrict__ proj, int64_t ld, const float* __restrict__ conv_w, int taps_rt, const float* __restrict__ conv_state,
     const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ slots, int n_tokens, int n_seqs, int G,
     int D, int H, int Dv, const float* __restrict__ dpre, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -779,16 +784,15 @@ __global__ void __launch_bounds__(GP_BLOCK) gdrc_prepare_kernel(
     int* status) {
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ float qk_s[2 * LP_MAX_D];
     const int taps = TAPS ? TAPS : taps_rt;
-    const int lane = threadIdx.x & 31;
-    const int64_t item = (int64_t)blockIdx.x * (GP_BLOCK / 32) + (threadIdx.x >> 5);
-    if (item >= (int64_t)n_tokens * H) return;
-    const int t = (int)(item / H), h = (int)(item - (int64_t)t * H);
-    const int hk = h / (H / G);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int t = (int)(blockIdx.x / G), hk = (int)(blockIdx.x - (int64_t)t * G);
+    const int per_key = H / G;
     const int nqk = G * D, C = 2 * nqk + H * Dv;
     const int seq = seq_of_token[t];
     if (seq < 0 || seq >= n_seqs) {
-        if (lane == 0 && h == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        if (threadIdx.x == 0 && hk == 0) imp_report(status, IMP_BAD_SEQUENCE);
         return;
     }
     const int start = q_start[seq];
@@ -815,38 +819,46 @@ __global__ void __launch_bounds__(GP_BLOCK) gdrc_prepare_kernel(
         }
         return silu_f(acc);
     };
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) qk_s[i] = channel(i < D ? hk * D + i : nqk + hk * D + (i - D));
+    __syncthreads();
     float qq[LP_PER], kk[LP_PER], sq = 0.f, sk = 0.f;
 #pragma unroll
     for (int i = 0; i < LP_PER; ++i) {
         const int d = lane + i * 32;
-        qq[i] = d < D ? channel(hk * D + d) : 0.f;
-        kk[i] = d < D ? channel(nqk + hk * D + d) : 0.f;
+        qq[i] = d < D ? qk_s[d] : 0.f;
+        kk[i] = d < D ? qk_s[D + d] : 0.f;
         sq = fmaf(qq[i], qq[i], sq);
         sk = fmaf(kk[i], kk[i], sk);
     }
     sq = warp_sum(sq);
     sk = warp_sum(sk);
     const float rq = rsqrtf(sq + unit_eps) * rsqrtf((float)D), rk = rsqrtf(sk + unit_eps);
-    const float beta = 1.f / (1.f + expf(-to_float(proj[(int64_t)t * ld + C + h])));
-    const float rate = expf(a_log[h]);
-    const int64_t o = ((int64_t)t * H + h) * D;
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < LP_PER; ++i) {
-        const int d = lane + i * 32;
-        if (d < D) {
-            const float a = qq[i] * rq, b = kk[i] * rk;
-            q[o + d] = a;
-            kw[o + d] = b;
-            w[o + d] = expf(-rate * softplus_f(dpre[(int64_t)t * H * D + h * D + d] + dt_bias[h * D + d]));
-            dot = fmaf(a, b, dot);
-        }
+        qq[i] *= rq;
+        kk[i] *= rk;
+        dot = fmaf(qq[i], kk[i], dot);
     }
-    for (int d = lane; d < Dv; d += 32) v[((int64_t)t * H + h) * Dv + d] = channel(2 * nqk + h * Dv + d);
     dot = warp_sum(dot);
-    if (lane == 0) {
-        scal[((int64_t)t * H + h) * 2] = beta * dot;
-        scal[((int64_t)t * H + h) * 2 + 1] = beta;
+    for (int h = hk * per_key + warp; h < (hk + 1) * per_key; h += n_warps) {
+        const float beta = 1.f / (1.f + expf(-to_float(proj[(int64_t)t * ld + C + h])));
+        const float rate = expf(a_log[h]);
+        const int64_t o = ((int64_t)t * H + h) * D;
+#pragma unroll
+        for (int i = 0; i < LP_PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < D) {
+                q[o + d] = qq[i];
+                kw[o + d] = kk[i];
+                w[o + d] = expf(-rate * softplus_f(dpre[(int64_t)t * H * D + h * D + d] + dt_bias[h * D + d]));
+            }
+        }
+        for (int d = lane; d < Dv; d += 32) v[((int64_t)t * H + h) * Dv + d] = channel(2 * nqk + h * Dv + d);
+        if (lane == 0) {
+            scal[((int64_t)t * H + h) * 2] = beta * dot;
+            scal[((int64_t)t * H + h) * 2 + 1] = beta;
+        }
     }
 }
 
@@ -894,9 +906,12 @@ IMP_API int imp_gdrc_prepare(const void* proj, int64_t ld, const float* conv_w, 
                   "imp_gdrc_prepare: bad sizes (heads %d over %d key heads, key size %d of at most %d)", H, G, D, LP_MAX_D);
     IMP_CHECK_ARG(ld >= (int64_t)2 * G * D + (int64_t)H * Dv + H, "imp_gdrc_prepare: the projection's rows are too short");
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(lp_grid((int64_t)n_tokens * H));
+    IMP_CHECK_ARG((int64_t)n_tokens * G <= 0x7fffffff, "imp_gdrc_prepare: too many tokens");
+    const dim3 grid((unsigned)((int64_t)n_tokens * G));
+    // a warp per value head of the key head, and enough threads for the key head's 2 D channels to be made in one or two rounds
+    const int n_warps = std::max(std::min(H / G, GC_MAX_WARPS), std::min((D + 31) / 32, 4));
 #define GDRC_PREPARE(TA, TAPS)                                                                                                          \
-    imp_launch(gdrc_prepare_kernel<TA, TAPS>, grid, dim3(GP_BLOCK), 0, s, (const TA*)proj, ld, conv_w, taps, conv_state, seq_of_token, q_start, \
+    imp_launch(gdrc_prepare_kernel<TA, TAPS>, grid, dim3(32 * n_warps), 0, s, (const TA*)proj, ld, conv_w, taps, conv_state, seq_of_token, q_start, \
                slots, n_tokens, n_seqs, G, D, H, Dv, dpre, a_log, dt_bias, unit_eps, q, kw, w, v, scal, status)
 #define GDRC_PREPARE_T(TA)                       \
     do {                                         \

@@ -344,8 +344,8 @@ static bool bias_attention_mma(Step& st, Tensor out, const Tensor& q, const Atte
     // portions of 64 tokens and more on the tensor-memory kernel in tiles of 128, where it takes the geometry and the
     // caller has the table in that kernel's padded layout
     const Tiles& wide = st.tiles.at((size_t)tiling_ids[1]);
-    const bool tc = wide.count && (!ex.bias || ex.bias_pad_l2) && prefill_tc_supported(q, out, g, c) &&
-                    tc_variant(g.dh).bias_pad() == ex.pad;
+    const bool tc = wide.count && prefill_tc_supported(q, out, g, c) &&
+                    (!ex.bias || (ex.bias_pad_l2 && tc_variant(g.dh).bias_pad() == ex.pad));   // a sink alone needs no table
     if (tc) {
         TcVariant& tlib = tc_variant(g.dh);
         check_variant(rt,

@@ -14,13 +14,15 @@
 // Norm statistics, angles, the rotation and the per-head factors are 32-bit; results are rounded once.
 #include "common.cuh"
 
-constexpr int QP_BLOCK = 128;
+constexpr int QP_BLOCK = 256;
+constexpr int QP_WARPS = QP_BLOCK / 32;
+constexpr int QP_UNITS = 16;     // units of one token a CTA takes, two a warp: the token's angles are made once for all of them
 constexpr int QP_MAX_D = 512;
-constexpr int QP_PER = QP_MAX_D / 32;
 
-// One warp per (token, unit); units: Hq query heads, then Hkv key heads, then Hkv value heads.
+// A CTA per (token, group of QP_UNITS units), a warp per unit; units: Hq query heads, then Hkv key heads, then Hkv value
+// heads; PER entries of a head a lane (the cache's head size is at most 32 * PER).
 // proj: [T, ld] with columns [q: Hq*D | k: Hkv*D | v: Hkv*Dv | ...].  inv_freq: [rot/2] float32 (angle = pos * inv_freq[i]).
-template <typename TA>
+template <typename TA, int PER>
 __global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
     const TA* __restrict__ proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* __restrict__ q_norm_w,
     const float* __restrict__ k_norm_w, float eps, int v_norm, const float* __restrict__ inv_freq, int rot,
@@ -29,82 +31,87 @@ __global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
     TA* __restrict__ v_cache, int page_size, int num_pages, int* status) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ float rot_s[QP_BLOCK / 32][QP_MAX_D];
-    const int lane = threadIdx.x & 31;
+    __shared__ float rot_s[QP_WARPS][32 * PER];
+    __shared__ float cos_s[16 * PER], sin_s[16 * PER];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int units = Hq + 2 * Hkv;
-    const int64_t item = (int64_t)blockIdx.x * (QP_BLOCK / 32) + (threadIdx.x >> 5);
-    if (item >= (int64_t)n_tokens * units) return;
-    const int64_t t = item / units;
-    const int unit = (int)(item - t * units);
+    const int64_t t = blockIdx.x;
     const int seq = seq_of_token[t], pos = positions[t];
     if (seq < 0 || seq >= n_seqs || pos < 0 || pos / page_size >= bt_stride) {
-        if (lane == 0 && unit == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
+        if (threadIdx.x == 0 && blockIdx.y == 0) imp_report(status, seq < 0 || seq >= n_seqs ? IMP_BAD_SEQUENCE : IMP_BAD_POSITION);
         return;
     }
-    const bool is_q = unit < Hq, is_v = unit >= Hq + Hkv;
-    const int head = is_q ? unit : is_v ? unit - Hq - Hkv : unit - Hq;
-    const int n = is_v ? Dv : D;
-    const TA* src = proj + t * ld + (is_q ? (int64_t)head * D : is_v ? (int64_t)Hq * D + (int64_t)Hkv * D + (int64_t)head * Dv
-                                                                     : (int64_t)Hq * D + (int64_t)head * D);
-    TA* dst;
-    if (is_q) {
-        dst = q_out + t * q_ld + (int64_t)head * Dc;
-    } else {
-        const int page = block_table[(int64_t)seq * bt_stride + pos / page_size];
-        if (page < 0 || page >= num_pages) {
-            if (lane == 0) imp_report(status, IMP_BAD_PAGE);
-            return;
-        }
-        TA* cache = is_v ? v_cache : k_cache;
-        if (!cache) return;
-        dst = cache + (((int64_t)page * Hkv + head) * page_size + pos % page_size) * Dc;   // pages are [page][kv head][slot][entry]
+    const int half = rot / 2;
+    const int u_begin = blockIdx.y * QP_UNITS, u_end = min(units, u_begin + QP_UNITS);
+    if (rot > 0 && u_begin < Hq + Hkv) {     // a group of value heads rotates nothing
+        for (int i = threadIdx.x; i < half; i += QP_BLOCK) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
     }
-    float x[QP_PER], ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < QP_PER; ++i) {
-        const int d = lane + i * 32;
-        x[i] = d < n ? to_float(src[d]) : 0.f;
-        ss = fmaf(x[i], x[i], ss);
-    }
-    const float* nw = is_q ? q_norm_w : is_v ? nullptr : k_norm_w;
-    const bool normed = is_v ? v_norm != 0 : nw != nullptr;
-    if (normed) {
-        ss = warp_sum(ss);
-        const float r = rsqrtf(ss / (float)n + eps);
-#pragma unroll
-        for (int i = 0; i < QP_PER; ++i) {
-            const int d = lane + i * 32;
-            if (d < n) x[i] = x[i] * r * (nw ? nw[d] : 1.f);
+    __syncthreads();
+    const int page = block_table[(int64_t)seq * bt_stride + pos / page_size];
+    for (int unit = u_begin + warp; unit < u_end; unit += QP_WARPS) {
+        const bool is_q = unit < Hq, is_v = unit >= Hq + Hkv;
+        const int head = is_q ? unit : is_v ? unit - Hq - Hkv : unit - Hq;
+        const int n = is_v ? Dv : D;
+        const TA* src = proj + t * ld + (is_q ? (int64_t)head * D : is_v ? (int64_t)Hq * D + (int64_t)Hkv * D + (int64_t)head * Dv
+                                                                         : (int64_t)Hq * D + (int64_t)head * D);
+        TA* dst;
+        if (is_q) {
+            dst = q_out + t * q_ld + (int64_t)head * Dc;
+        } else {
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0) imp_report(status, IMP_BAD_PAGE);
+                continue;
+            }
+            TA* cache = is_v ? v_cache : k_cache;
+            if (!cache) continue;
+            dst = cache + (((int64_t)page * Hkv + head) * page_size + pos % page_size) * Dc;   // pages are [page][kv head][slot][entry]
         }
-    }
-    if (!is_v && rot > 0) {
-        // entry d < rot/2 pairs with d + rot/2, which another lane holds: the head goes through shared memory once
-        float* row = rot_s[threadIdx.x >> 5];
-        const int half = rot / 2;
+        float x[PER], ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < QP_PER; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + i * 32;
-            if (d < rot) row[d] = x[i];
+            x[i] = d < n ? to_float(src[d]) : 0.f;
+            ss = fmaf(x[i], x[i], ss);
         }
-        __syncwarp();
+        const float* nw = is_q ? q_norm_w : is_v ? nullptr : k_norm_w;
+        const bool normed = is_v ? v_norm != 0 : nw != nullptr;
+        if (normed) {
+            ss = warp_sum(ss);
+            const float r = rsqrtf(ss / (float)n + eps);
 #pragma unroll
-        for (int i = 0; i < QP_PER; ++i) {
-            const int d = lane + i * 32;
-            if (d < rot) {
-                const int fi = d < half ? d : d - half;
-                const float partner = row[d < half ? d + half : d - half];
-                float sn, cs;
-                sincosf((float)pos * inv_freq[fi], &sn, &cs);
-                // (u, v) -> (u cos - v sin, v cos + u sin)
-                x[i] = d < half ? x[i] * cs - partner * sn : x[i] * cs + partner * sn;
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + i * 32;
+                if (d < n) x[i] = x[i] * r * (nw ? nw[d] : 1.f);
             }
         }
-    }
-    const float mult = (is_q && head_mult) ? head_mult[head] : 1.f;
+        if (!is_v && rot > 0) {
+            // entry d < rot/2 pairs with d + rot/2, which another lane holds: the head goes through shared memory once
+            float* row = rot_s[warp];
 #pragma unroll
-    for (int i = 0; i < QP_PER; ++i) {
-        const int d = lane + i * 32;
-        if (d < Dc) dst[d] = from_float<TA>(d < n ? x[i] * mult : 0.f);
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + i * 32;
+                if (d < rot) row[d] = x[i];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + i * 32;
+                if (d < rot) {
+                    const int fi = d < half ? d : d - half;
+                    const float partner = row[d < half ? d + half : d - half];
+                    const float sn = sin_s[fi], cs = cos_s[fi];
+                    // (u, v) -> (u cos - v sin, v cos + u sin)
+                    x[i] = d < half ? x[i] * cs - partner * sn : x[i] * cs + partner * sn;
+                }
+            }
+            __syncwarp();     // the row is written again for the warp's next unit
+        }
+        const float mult = (is_q && head_mult) ? head_mult[head] : 1.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = lane + i * 32;
+            if (d < Dc) dst[d] = from_float<TA>(d < n ? x[i] * mult : 0.f);
+        }
     }
 }
 
@@ -191,16 +198,22 @@ IMP_API int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, 
     IMP_CHECK_ARG(ld >= (int64_t)(Hq + Hkv) * D + (int64_t)Hkv * Dv && q_ld >= (int64_t)Hq * Dc, "imp_qkv_prepare: rows too short");
     IMP_CHECK_ARG(page_size > 0 && num_pages > 0, "imp_qkv_prepare: bad cache geometry");
     cudaStream_t s = (cudaStream_t)stream;
-    const int64_t items = (int64_t)n_tokens * (Hq + 2 * Hkv);
-    const dim3 grid((unsigned)((items + QP_BLOCK / 32 - 1) / (QP_BLOCK / 32)));
-    if (act_dtype == IMP_F32)
-        imp_launch(qkv_prepare_kernel<float>, grid, dim3(QP_BLOCK), 0, s, (const float*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w, k_norm_w, eps,
-                   v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (float*)q_out, q_ld, (float*)k_cache,
-                   (float*)v_cache, page_size, num_pages, status);
-    else
-        imp_launch(qkv_prepare_kernel<__nv_bfloat16>, grid, dim3(QP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w,
-                   k_norm_w, eps, v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (__nv_bfloat16*)q_out,
-                   q_ld, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_size, num_pages, status);
+    const dim3 grid((unsigned)n_tokens, (unsigned)((Hq + 2 * Hkv + QP_UNITS - 1) / QP_UNITS));
+#define QP_LAUNCH(TA, PER)                                                                                                                    \
+    imp_launch(qkv_prepare_kernel<TA, PER>, grid, dim3(QP_BLOCK), 0, s, (const TA*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w, k_norm_w, eps, \
+               v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (TA*)q_out, q_ld, (TA*)k_cache,     \
+               (TA*)v_cache, page_size, num_pages, status)
+#define QP_LAUNCH_PER(TA)                       \
+    do {                                        \
+        if (Dc <= 64) QP_LAUNCH(TA, 2);         \
+        else if (Dc <= 128) QP_LAUNCH(TA, 4);   \
+        else if (Dc <= 256) QP_LAUNCH(TA, 8);   \
+        else QP_LAUNCH(TA, 16);                 \
+    } while (0)
+    if (act_dtype == IMP_F32) QP_LAUNCH_PER(float);
+    else QP_LAUNCH_PER(__nv_bfloat16);
+#undef QP_LAUNCH_PER
+#undef QP_LAUNCH
     IMP_RETURN_LAUNCH();
 }
 

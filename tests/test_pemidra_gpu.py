@@ -401,6 +401,37 @@ def test_a_loud_key_at_the_chunk_edge_is_seen_inside_and_not_outside(dtype):
         assert (off[395:403] - want[395:403]).abs().max() > 0.3 * want[395:403].abs().max()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim,vdim,chunk", [(64, 64, 200), (128, 128, 70), (128, 96, 128), (64, 48, 333)])
+def test_gated_head_attention_long_portions_with_chunk_edges_inside_tiles(dtype, dim, vdim, chunk):
+    """Portions of 64 tokens and more, which the tiled prefill kernels take, with chunk edges in the middle of a tile of keys
+    and of a tile of queries, rows whose chunk begins after a tile's last key, a portion that starts at an edge and one
+    that ends on it; beside a second sequence that brings single tokens."""
+    case = dict(d=64, heads=4, kv_heads=2, dim=dim, vdim=vdim, chunk=chunk, rot=dim // 2, base=1e4, page=16)
+    bench, part, c, W = attention_setup(dtype, case)
+    T = chunk + 270
+    x, y = rnd(T, 64, seed=70).to(dtype), rnd(5, 64, seed=71).to(dtype)
+    want, want_y = P.gated_head_attention(x.double(), W, "m.", c, EPS), P.gated_head_attention(y.double(), W, "m.", c, EPS)
+    ctx = bench.prepare([("w", [1] * T, [])])
+    close(run_part(bench, part, x, ctx, bench.cache_view(0)), want, dtype, "whole")
+    bench.commit()
+    bench.end("w")
+    done, outs = 0, []
+    for i, n in enumerate((chunk, 64, 130, 3, T - chunk - 197)):
+        es, parts = [("p", [1] * n, [])], [x[done:done + n]]
+        if i < 5:
+            es.insert(0, ("s", [1], []))               # the single token leads the step
+            parts.insert(0, y[i:i + 1])
+        ctx = bench.prepare(es)
+        o = run_part(bench, part, torch.cat(parts), ctx, bench.cache_view(0))
+        bench.commit()
+        close(o[:1], want_y[i:i + 1], dtype, f"single token {i}")
+        outs.append(o[1:])
+        done += n
+    assert done == T
+    close(torch.cat(outs), want, dtype, "portions")
+
+
 # --------------------------------------------------------------- whole models
 def attn_cfg(heads, kv, dim, vdim, chunk, rot, base=10000.0, scale=None):
     c = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale or 1.5 / math.sqrt(dim)}
