@@ -871,7 +871,7 @@ def run_arch_beside(args, arch, config_of):
 
 
 def run_reference(args):
-    """The one offline install the contract describes is attempted once (it cannot succeed: the reference is a
+    """The one offline install of the reference is attempted once (it cannot succeed: the reference is a
     CMake C++/CUDA project without setup.py or pyproject.toml, it needs CUDA >= 13.1 where this image has 12.9,
     and its configure step fetches googletest, CUTLASS and two more projects from the network)."""
     why = "kekzl/imp is not pip-installable (no setup.py/pyproject.toml; CMake needs CUDA >= 13.1 and network fetches)"
