@@ -190,3 +190,35 @@ class PemidraConfig(ModelConfig):
     @property
     def num_hidden_layers(self) -> int:
         return len(self.raw["layers"])
+
+
+class NizoraxConfig(ModelConfig):
+    """Nizorax (`"architecture": "Nizorax"`): `vocab`, `width`, `norm.eps`, `embedding.scale`, `logit_scale`, `canon.taps` (the
+    short convolution added to what every sublayer reads), a list `layers`, each entry with `type` ("attention" or
+    "lightning"), the mixer's sizes and constants under `mixer`, and `mlp` (`{"kind": "dense", "ff"}`,
+    `{"kind": "moe", "expert": {"ff"}, "router": {"experts", "top", "scale", "groups": {"count", "keep"}}, "shared": {"ff"} | null}`
+    or null); optionally `loop` (`{"start", "stop", "times"}`): layers start .. stop-1 run `times` times with the same weights."""
+
+    KNOWN_KEYS = ("architecture", "vocab", "width", "norm", "embedding", "logit_scale", "canon", "layers", "loop", "torch_dtype",
+                  "dtype", "eos_token_id", "bos_token_id", "max_positions")
+
+    @property
+    def vocab_size(self) -> int:
+        return int(self.raw["vocab"])
+
+    @property
+    def hidden_size(self) -> int:
+        return int(self.raw["width"])
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.raw["layers"])
+
+    def run_order(self):
+        """Layer indices in the order they run (a repeated run of layers appears `times` times)."""
+        n = len(self.raw["layers"])
+        loop = self.raw.get("loop")
+        if not loop:
+            return list(range(n))
+        a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+        return list(range(a)) + list(range(a, b)) * times + list(range(b, n))

@@ -17,12 +17,13 @@ import os
 from typing import Any, Callable, Dict, Type
 
 from .. import capi
-from .model_config import ConfigError, KazedraConfig, KuzipelConfig, ModelConfig, PemidraConfig, Qwen3Config, architecture_name
+from .model_config import (ConfigError, KazedraConfig, KuzipelConfig, ModelConfig, NizoraxConfig, PemidraConfig, Qwen3Config,
+                           architecture_name)
 
 # architectures registered from Python: name -> (config class, plan function, C callback kept alive)
 _PY_ARCHS: Dict[str, tuple] = {}
 _BUILTIN_CONFIGS: Dict[str, Type[ModelConfig]] = {"Qwen3ForCausalLM": Qwen3Config, "Kazedra": KazedraConfig, "Kuzipel": KuzipelConfig,
-                                                   "Pemidra": PemidraConfig}
+                                                   "Pemidra": PemidraConfig, "Nizorax": NizoraxConfig}
 
 
 def parse_config_dict(d: Dict[str, Any], where: str = "config.json") -> Dict[str, Any]:

@@ -401,6 +401,29 @@ IMP_API int imp_gdr_scan(const float* qn, const float* kn, const float* vc, cons
     IMP_RETURN_LAUNCH();
 }
 
+
+// The same read-out with one norm over the whole row: y[t, :] = o[t, :] / sqrt(mean over all n of o^2 + eps) * w * act(gate[t, :]),
+// the heads side by side (n = H * Dv); a CTA per token, sums in 32-bit in an order the row's size fixes.
+template <typename TA>
+__global__ void __launch_bounds__(256) lsr_output_row_kernel(TA* __restrict__ y, const float* __restrict__ o, const TA* __restrict__ gate, int64_t gate_ld,
+                                                             const float* __restrict__ w, int act, float eps, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int64_t t = blockIdx.x;
+    const float* x = o + t * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+    const float r = rsqrtf(block_sum(ss, scratch) / (float)n + eps);
+    const TA* gt = gate + t * gate_ld;
+    TA* dst = y + t * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float g = to_float(gt[i]);
+        const float a = act == 0 ? silu_f(g) : 1.f / (1.f + expf(-g));
+        dst[i] = from_float<TA>(x[i] * r * (w ? w[i] : 1.f) * a);
+    }
+}
+
 // The read-out's norm and gate.  w: float32 weight or null; w_head_stride: 0 for one vector [Dv] shared by the heads, Dv for
 // a vector [H * Dv]; gate_act: 0 silu, 1 sigmoid.
 IMP_API int imp_gdr_output_ex(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, int w_head_stride, int gate_act,
@@ -419,6 +442,21 @@ IMP_API int imp_gdr_output_ex(void* y, const float* o, const void* gate, int64_t
                    w_head_stride, gate_act, eps, n_tokens, H, Dv);
     IMP_RETURN_LAUNCH();
 }
+
+// The read-out normalised over the whole row of n = H * Dv values (w: float32 [n] or null; gate_act: 0 silu, 1 sigmoid).
+IMP_API int imp_lsr_output_row(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, int gate_act, float eps, int n_tokens,
+                               int n, int act_dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(y && o && gate && n > 0 && gate_ld >= n && (gate_act == 0 || gate_act == 1), "imp_lsr_output_row: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == IMP_F32)
+        imp_launch(lsr_output_row_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (float*)y, o, (const float*)gate, gate_ld, w, gate_act, eps, n);
+    else
+        imp_launch(lsr_output_row_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, s, (__nv_bfloat16*)y, o, (const __nv_bfloat16*)gate, gate_ld, w,
+                   gate_act, eps, n);
+    IMP_RETURN_LAUNCH();
+}
+
 
 IMP_API int imp_gdr_output(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, float eps, int n_tokens, int H,
                            int Dv, int act_dtype, void* stream) {
@@ -682,10 +720,11 @@ IMP_API int imp_lsr_scan(int mode, const float* kw, const float* q, const float*
 constexpr int LP_MAX_D = 256;
 constexpr int LP_PER = LP_MAX_D / 32;
 
-// Retention: proj columns [q: H*D | k: H*D | v: H*Dv | ...]; q as projected, kw = k * k_scale, scal = (q . kw, 0).
+// Retention: proj columns [q: H*D | k: H*D | v: H*Dv | ...]; q = f(q projected), kw = f(k) * k_scale, v = f(v), scal = (q . kw, 0);
+// f the identity (act 0) or silu (act 1), in 32-bit.
 template <typename TA>
 __global__ void __launch_bounds__(GP_BLOCK) retention_prepare_kernel(const TA* __restrict__ proj, int64_t ld, int n_tokens, int H, int D, int Dv,
-                                                                     float k_scale, float* __restrict__ q, float* __restrict__ kw,
+                                                                     float k_scale, int act, float* __restrict__ q, float* __restrict__ kw,
                                                                      float* __restrict__ v, float* __restrict__ scal) {
     pdl_wait();
     pdl_launch_dependents();
@@ -697,12 +736,17 @@ __global__ void __launch_bounds__(GP_BLOCK) retention_prepare_kernel(const TA* _
     const TA* row = proj + t * ld;
     float dot = 0.f;
     for (int d = lane; d < D; d += 32) {
-        const float qq = to_float(row[h * D + d]), kk = to_float(row[(int64_t)H * D + h * D + d]) * k_scale;
+        float qq = to_float(row[h * D + d]), kk = to_float(row[(int64_t)H * D + h * D + d]);
+        if (act == 1) qq = silu_f(qq), kk = silu_f(kk);
+        kk *= k_scale;
         q[(t * H + h) * D + d] = qq;
         kw[(t * H + h) * D + d] = kk;
         dot = fmaf(qq, kk, dot);
     }
-    for (int d = lane; d < Dv; d += 32) v[(t * H + h) * Dv + d] = to_float(row[(int64_t)2 * H * D + h * Dv + d]);
+    for (int d = lane; d < Dv; d += 32) {
+        const float vv = to_float(row[(int64_t)2 * H * D + h * Dv + d]);
+        v[(t * H + h) * Dv + d] = act == 1 ? silu_f(vv) : vv;
+    }
     dot = warp_sum(dot);
     if (lane == 0) {
         scal[(t * H + h) * 2] = dot;
@@ -864,18 +908,24 @@ __global__ void __launch_bounds__(GC_MAX_WARPS * 32) gdrc_prepare_kernel(
 
 static unsigned lp_grid(int64_t items) { return (unsigned)((items + GP_BLOCK / 32 - 1) / (GP_BLOCK / 32)); }
 
-IMP_API int imp_retention_prepare(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, float* q, float* kw, float* v,
-                                  float* scal, int act_dtype, void* stream) {
+IMP_API int imp_retention_prepare_ex(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, int act, float* q, float* kw,
+                                     float* v, float* scal, int act_dtype, void* stream) {
     if (n_tokens == 0) return 0;
-    IMP_CHECK_ARG(proj && q && kw && v && scal && H > 0 && D > 0 && Dv > 0 && ld >= (int64_t)2 * H * D + (int64_t)H * Dv, "imp_retention_prepare: bad argument");
+    IMP_CHECK_ARG(proj && q && kw && v && scal && H > 0 && D > 0 && Dv > 0 && ld >= (int64_t)2 * H * D + (int64_t)H * Dv && (act == 0 || act == 1),
+                  "imp_retention_prepare: bad argument");
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(lp_grid((int64_t)n_tokens * H));
     if (act_dtype == IMP_F32)
-        imp_launch(retention_prepare_kernel<float>, grid, dim3(GP_BLOCK), 0, s, (const float*)proj, ld, n_tokens, H, D, Dv, k_scale, q, kw, v, scal);
+        imp_launch(retention_prepare_kernel<float>, grid, dim3(GP_BLOCK), 0, s, (const float*)proj, ld, n_tokens, H, D, Dv, k_scale, act, q, kw, v, scal);
     else
-        imp_launch(retention_prepare_kernel<__nv_bfloat16>, grid, dim3(GP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, n_tokens, H, D, Dv, k_scale, q,
-                   kw, v, scal);
+        imp_launch(retention_prepare_kernel<__nv_bfloat16>, grid, dim3(GP_BLOCK), 0, s, (const __nv_bfloat16*)proj, ld, n_tokens, H, D, Dv, k_scale, act,
+                   q, kw, v, scal);
     IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_retention_prepare(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, float* q, float* kw, float* v,
+                                  float* scal, int act_dtype, void* stream) {
+    return imp_retention_prepare_ex(proj, ld, n_tokens, H, D, Dv, k_scale, 0, q, kw, v, scal, act_dtype, stream);
 }
 
 IMP_API int imp_gdelta_prepare(const void* proj, int64_t ld, const float* dlog, const float* w0, const float* a_bias, float decay_scale,

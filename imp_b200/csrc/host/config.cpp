@@ -2,6 +2,7 @@
 
 #include <sys/stat.h>
 
+#include <cmath>
 #include <fstream>
 #include <map>
 #include <mutex>
@@ -841,6 +842,283 @@ ModelPlan pemidra_plan(const PemidraConfig& cfg) {
     return plan;
 }
 
+// ------------------------------------------------------------------------------------ Nizorax
+NizoraxConfig NizoraxConfig::from_json(const Json& d, const std::string& where) {
+    NizoraxConfig c;
+    c.architecture = d.get_string("architecture", "Nizorax");
+    c.vocab_size = positive("vocab", require_int(d, "vocab", where), where);
+    c.hidden_size = positive("width", require_int(d, "width", where), where);
+    c.max_position_embeddings = positive("max_positions", d.get_int("max_positions", 1 << 20), where);
+    c.torch_dtype = d.get_string("torch_dtype", d.get_string("dtype", "bfloat16"));
+    if (c.torch_dtype != "bfloat16" && c.torch_dtype != "float32")
+        bad(where + ": torch_dtype '" + c.torch_dtype + "' is not supported (bfloat16 or float32)");
+    if (const Json* eos = d.find("eos_token_id")) {
+        if (eos->is_array()) {
+            for (const auto& e : eos->items())
+                if (e.is_int()) c.eos_token_ids.push_back((int)e.as_int());
+        } else if (eos->is_int()) {
+            c.eos_token_ids.push_back((int)eos->as_int());
+        }
+    }
+    c.bos_token_id = d.get_int("bos_token_id", -1);
+    c.raw = d;
+    c.norm_eps = require_float(require_object(d, "norm", where), "eps", where + ": norm");
+    if (!(c.norm_eps > 0)) bad(where + ": norm.eps must be positive");
+    auto optional_object = [&](const Json& in, const char* key, const std::string& w) -> const Json* {
+        const Json* v = in.find(key);
+        if (!v || v->is_null()) return nullptr;
+        if (!v->is_object()) bad(w + ": '" + key + "' must be an object or null");
+        return v;
+    };
+    if (const Json* e = optional_object(d, "embedding", where)) c.embedding_scale = e->get_double("scale", 1.0);
+    c.logit_scale = d.get_double("logit_scale", 1.0);
+    if (const Json* cn = optional_object(d, "canon", where)) {
+        c.canon_taps = positive("taps", require_int(*cn, "taps", where + ": canon"), where + ": canon");
+        if (c.canon_taps > 64) bad(where + ": canon.taps must be at most 64");
+    }
+    const Json& layers = require(d, "layers", where);
+    if (!layers.is_array() || layers.size() == 0) bad(where + ": 'layers' must be a non-empty list");
+    int i = 0;
+    for (const Json& lj : layers.items()) {
+        const std::string lw = where + ": layers[" + std::to_string(i++) + "]";
+        if (!lj.is_object()) bad(lw + " must be an object");
+        Layer l;
+        l.type = lj.get_string("type", "");
+        const Json& m = require_object(lj, "mixer", lw);
+        const std::string mw = lw + ".mixer";
+        l.heads = positive("heads", require_int(m, "heads", mw), mw);
+        l.dim = positive("dim", require_int(m, "dim", mw), mw);
+        l.vdim = positive("vdim", m.get_int("vdim", l.dim), mw);
+        if (l.type == "attention") {
+            l.kv_heads = positive("kv_heads", m.get_int("kv_heads", l.heads), mw);
+            if (l.heads % l.kv_heads) bad(mw + ": " + std::to_string(l.heads) + " heads are not a multiple of " + std::to_string(l.kv_heads) + " kv_heads");
+            l.diff = require_float(m, "diff", mw);
+            l.scale = m.find("scale") ? require_float(m, "scale", mw) : 1.0 / std::sqrt((double)l.dim);
+            if (!(l.scale > 0)) bad(mw + ": scale must be positive");
+            if (const Json* mask = optional_object(m, "mask", mw)) l.window = positive("size", require_int(*mask, "size", mw + ".mask"), mw + ".mask");
+            if (const Json* rot = optional_object(m, "rot", mw)) {
+                const std::string rw = mw + ".rot";
+                l.rot_base = require_float(*rot, "base", rw);
+                l.rot_dims = positive("dims", require_int(*rot, "dims", rw), rw);
+                if (!(l.rot_base > 0)) bad(rw + ": base must be positive");
+                if (l.rot_dims % 2 || l.rot_dims > l.dim) bad(rw + ": dims " + std::to_string(l.rot_dims) + " must be even and at most dim " + std::to_string(l.dim));
+                if (const Json* sc = optional_object(*rot, "scaling", rw)) {
+                    const std::string sw = rw + ".scaling";
+                    l.rot_scaled = true;
+                    l.rot_factor = require_float(*sc, "factor", sw);
+                    l.rot_low = require_float(*sc, "low", sw);
+                    l.rot_high = require_float(*sc, "high", sw);
+                    l.rot_original = require_float(*sc, "original", sw);
+                    if (!(l.rot_factor > 0) || !(l.rot_low > 0) || !(l.rot_high > l.rot_low) || !(l.rot_original > 0))
+                        bad(sw + ": factor > 0, 0 < low < high and original > 0 are required");
+                }
+            }
+        } else if (l.type == "lightning") {
+            l.kv_heads = l.heads;
+            const Json& dj = require(m, "decay", mw);
+            if (!dj.is_array() || (int64_t)dj.size() != l.heads) bad(mw + ": 'decay' must list a number per head");
+            for (const Json& e : dj.items()) {
+                if (!e.is_number()) bad(mw + ": 'decay' must list numbers");
+                l.decay.push_back(e.as_double());
+            }
+        } else {
+            bad(lw + ": unknown layer type '" + l.type + "' (known: attention, lightning)");
+        }
+        if (const Json* f = optional_object(lj, "mlp", lw)) {
+            const std::string fw = lw + ".mlp";
+            l.mlp = f->get_string("kind", "");
+            if (l.mlp == "dense") {
+                l.ff = positive("ff", require_int(*f, "ff", fw), fw);
+            } else if (l.mlp == "moe") {
+                l.expert_ff = positive("ff", require_int(require_object(*f, "expert", fw), "ff", fw + ".expert"), fw + ".expert");
+                const Json& r = require_object(*f, "router", fw);
+                const std::string rw = fw + ".router";
+                l.experts = positive("experts", require_int(r, "experts", rw), rw);
+                l.top = positive("top", require_int(r, "top", rw), rw);
+                if (l.top > l.experts) bad(rw + ": top " + std::to_string(l.top) + " exceeds the " + std::to_string(l.experts) + " experts");
+                l.route_scale = r.get_double("scale", 1.0);
+                if (const Json* g = optional_object(r, "groups", rw)) {
+                    l.groups = positive("count", require_int(*g, "count", rw + ".groups"), rw + ".groups");
+                    l.keep = positive("keep", require_int(*g, "keep", rw + ".groups"), rw + ".groups");
+                    if (l.experts % l.groups || l.keep > l.groups || l.top > l.keep * (l.experts / l.groups))
+                        bad(rw + ".groups: count must divide the experts, keep be at most count, and the kept groups hold `top` experts");
+                }
+                if (const Json* sh = optional_object(*f, "shared", fw)) l.shared_ff = positive("ff", require_int(*sh, "ff", fw + ".shared"), fw + ".shared");
+            } else {
+                bad(fw + ": unknown kind '" + l.mlp + "' (known: dense, moe)");
+            }
+        }
+        c.layers.push_back(l);
+    }
+    c.num_hidden_layers = (int64_t)c.layers.size();
+    if (const Json* lp = optional_object(d, "loop", where)) {
+        c.has_loop = true;
+        c.loop_start = require_int(*lp, "start", where + ": loop");
+        c.loop_stop = require_int(*lp, "stop", where + ": loop");
+        c.loop_times = positive("times", require_int(*lp, "times", where + ": loop"), where + ": loop");
+        if (c.loop_start < 0 || c.loop_stop <= c.loop_start || c.loop_stop > c.num_hidden_layers)
+            bad(where + ": loop: 0 <= start < stop <= " + std::to_string(c.num_hidden_layers) + " is required, got " + std::to_string(c.loop_start) +
+                " and " + std::to_string(c.loop_stop));
+    }
+    return c;
+}
+
+Json NizoraxConfig::to_json() const {
+    Json j = raw.is_object() ? raw : Json::object();
+    j["architecture"] = architecture;
+    j["vocab"] = vocab_size;
+    j["width"] = hidden_size;
+    j["torch_dtype"] = torch_dtype;
+    j.erase("dtype");
+    return j;
+}
+
+std::vector<int> NizoraxConfig::run_order() const {
+    std::vector<int> o;
+    const int L = (int)layers.size();
+    const int a = has_loop ? (int)loop_start : L, b = has_loop ? (int)loop_stop : L;
+    for (int i = 0; i < a; ++i) o.push_back(i);
+    for (int64_t pass = 0; has_loop && pass < loop_times; ++pass)
+        for (int i = a; i < b; ++i) o.push_back(i);
+    for (int i = b; i < L; ++i) o.push_back(i);
+    return o;
+}
+
+// Layer i's tensors are 'l<i>.norm1', 'l<i>.norm1b' (the norms before and after the mixer, each with '.b'), 'l<i>.canon1',
+// 'l<i>.mix.*', and with a feed-forward 'l<i>.norm2', 'l<i>.norm2b', 'l<i>.canon2', 'l<i>.mlp.*'.  A layer that runs
+// several times gets a cache and a state per run.
+ModelPlan nizorax_plan(const NizoraxConfig& cfg) {
+    const int64_t d = cfg.hidden_size;
+    ModelPlan plan;
+    plan.architecture = cfg.architecture;
+    plan.hidden_size = d;
+    plan.vocab_size = cfg.vocab_size;
+    plan.max_positions = cfg.max_position_embeddings;
+    auto norm = [&](const std::string& tensor) {
+        PartSpec n;
+        n.kind = "layernorm";
+        n.params["size"] = d;
+        n.params["eps"] = cfg.norm_eps;
+        n.params["bias"] = true;
+        n.tensors = {{"weight", tensor}, {"bias", tensor + ".b"}};
+        return n;
+    };
+    auto conv = [&](const std::string& tensor) {
+        PartSpec c;
+        c.kind = "residual_conv";
+        c.params["hidden_size"] = d;
+        c.params["taps"] = cfg.canon_taps;
+        c.tensors = {{"weight", tensor}};
+        return c;
+    };
+    const bool has_conv = cfg.canon_taps > 0;
+    for (size_t i = 0; i < cfg.layers.size(); ++i) {
+        const NizoraxConfig::Layer& l = cfg.layers[i];
+        const std::string p = "l" + std::to_string(i) + ".", a = p + "mix.", f = p + "mlp.";
+        PartSpec mixer;
+        mixer.params["hidden_size"] = d;
+        mixer.params["num_heads"] = l.heads;
+        mixer.params["value_dim"] = l.vdim;
+        mixer.params["norm_eps"] = cfg.norm_eps;
+        if (l.type == "attention") {
+            mixer.kind = "differential_attention";
+            mixer.params["num_kv_heads"] = l.kv_heads;
+            mixer.params["head_dim"] = l.dim;
+            mixer.params["scale"] = l.scale;
+            mixer.params["lambda_init"] = l.diff;
+            mixer.params["window"] = l.window;
+            mixer.params["rot_dims"] = l.rot_dims;
+            mixer.params["rot_base"] = l.rot_base;
+            mixer.params["rot_pairing"] = "neighbours";
+            if (l.rot_scaled) {
+                Json sc = Json::object();
+                sc["factor"] = l.rot_factor;
+                sc["low"] = l.rot_low;
+                sc["high"] = l.rot_high;
+                sc["original"] = l.rot_original;
+                mixer.params["rot_scaling"] = sc;
+            }
+            mixer.tensors = {{"q_proj", a + "q"}, {"k_proj", a + "k"}, {"v_proj", a + "v"}, {"lambda_q1", a + "lq1"}, {"lambda_k1", a + "lk1"},
+                             {"lambda_q2", a + "lq2"}, {"lambda_k2", a + "lk2"}, {"o_proj", a + "o"}};
+        } else {
+            mixer.kind = "retention";
+            mixer.params["key_dim"] = l.dim;
+            Json dec = Json::array();
+            for (double v : l.decay) dec.push(v);
+            mixer.params["decay"] = dec;
+            mixer.params["key_scale"] = 1.0;
+            mixer.params["qkv_act"] = "silu";
+            mixer.params["gate_act"] = "sigmoid";
+            mixer.params["norm_over"] = "row";
+            mixer.params["out_norm"] = true;
+            mixer.tensors = {{"q_proj", a + "q"}, {"k_proj", a + "k"}, {"v_proj", a + "v"}, {"gate_proj", a + "g"}, {"out_norm", a + "norm"}, {"o_proj", a + "o"}};
+        }
+        LayerSpec layer;
+        layer.block = "sandwich";
+        layer.block_params["has_ffn"] = !l.mlp.empty();
+        layer.block_params["input_conv"] = has_conv;
+        layer.parts = {{"mixer_norm", norm(p + "norm1")}};
+        if (has_conv) layer.parts.emplace_back("mixer_conv", conv(p + "canon1"));
+        layer.parts.emplace_back("mixer", mixer);
+        layer.parts.emplace_back("mixer_post_norm", norm(p + "norm1b"));
+        if (!l.mlp.empty()) {
+            PartSpec ffn;
+            ffn.params["hidden_size"] = d;
+            if (l.mlp == "dense") {
+                ffn.kind = "polynorm_mlp";
+                ffn.params["intermediate_size"] = l.ff;
+                ffn.params["norm_eps"] = cfg.norm_eps;
+                ffn.tensors = {{"up_proj", f + "up"}, {"down_proj", f + "down"}, {"coef", f + "act"}};
+            } else {
+                ffn.kind = "routed_experts";
+                ffn.params["num_experts"] = l.experts;
+                ffn.params["top_k"] = l.top;
+                ffn.params["expert_size"] = l.expert_ff;
+                ffn.params["shared_size"] = l.shared_ff;
+                ffn.params["router_bias"] = false;
+                ffn.params["shared_gate"] = false;
+                ffn.params["scores"] = "sigmoid";
+                ffn.params["weight_scale"] = l.route_scale;
+                ffn.params["num_groups"] = l.groups;
+                ffn.params["keep_groups"] = l.keep;
+                ffn.tensors = {{"router", f + "router"}};
+                for (int64_t e = 0; e < l.experts; ++e) {
+                    const std::string n = std::to_string(e), t = f + "e" + n + ".";
+                    ffn.tensors.emplace_back("gate_" + n, t + "gate");
+                    ffn.tensors.emplace_back("up_" + n, t + "up");
+                    ffn.tensors.emplace_back("down_" + n, t + "down");
+                }
+                if (l.shared_ff > 0) {
+                    ffn.tensors.emplace_back("shared_gate", f + "shared.gate");
+                    ffn.tensors.emplace_back("shared_up", f + "shared.up");
+                    ffn.tensors.emplace_back("shared_down", f + "shared.down");
+                }
+            }
+            layer.parts.emplace_back("ffn_norm", norm(p + "norm2"));
+            if (has_conv) layer.parts.emplace_back("ffn_conv", conv(p + "canon2"));
+            layer.parts.emplace_back("feed_forward", ffn);
+            layer.parts.emplace_back("ffn_post_norm", norm(p + "norm2b"));
+        }
+        plan.layers.push_back(layer);
+    }
+    if (cfg.has_loop) {
+        plan.has_order = true;
+        plan.order = cfg.run_order();
+    }
+    plan.embedding.kind = "token_embedding";
+    plan.embedding.params["vocab_size"] = cfg.vocab_size;
+    plan.embedding.params["hidden_size"] = d;
+    plan.embedding.params["scale"] = cfg.embedding_scale;
+    plan.embedding.tensors = {{"weight", "embed"}};
+    plan.final_norm = norm("final.norm");
+    plan.head.kind = "linear_head";
+    plan.head.params["vocab_size"] = cfg.vocab_size;
+    plan.head.params["hidden_size"] = d;
+    plan.head.params["scale"] = cfg.logit_scale;
+    plan.head.tensors = {{"weight", "head"}};
+    return plan;
+}
+
 // ------------------------------------------------------------------------------------ registry
 namespace {
 std::mutex g_arch_mutex;
@@ -879,6 +1157,13 @@ void ensure_builtin_archs() {
         };
         pm.plan = [](const Json& d) { return pemidra_plan(PemidraConfig::from_json(d, "config.json")); };
         archs()[pm.name] = pm;
+        Architecture nz;
+        nz.name = "Nizorax";
+        nz.parse_config = [](const Json& d, const std::string& where) -> std::shared_ptr<ModelConfig> {
+            return std::make_shared<NizoraxConfig>(NizoraxConfig::from_json(d, where));
+        };
+        nz.plan = [](const Json& d) { return nizorax_plan(NizoraxConfig::from_json(d, "config.json")); };
+        archs()[nz.name] = nz;
     });
 }
 }  // namespace

@@ -148,6 +148,44 @@ struct PemidraConfig : ModelConfig {
 // and `gate_rank` keys of a mixer fix them (random weights need them).
 ModelPlan pemidra_plan(const PemidraConfig& cfg);
 
+// Nizorax ("architecture": "Nizorax"): every sublayer stands between two layer norms (weight and bias),
+// x <- x + ln_b(sublayer(c(ln_a(x)))), and what it reads first gets a short causal convolution per channel added to itself
+// (c(u) = u + conv(u), `canon.taps` taps).  A layer's mixer is differential attention (two softmax maps per head over the
+// same values, grouped key/value heads, a sliding window, a rotation of neighbouring pairs with slowed long wavelengths) or
+// lightning (linear attention with a fixed decay per head).  The feed-forward is dense with a normalised polynomial as
+// activation, a mixture of gated experts (sigmoid scores, groups of experts, a shared expert), or absent.  A run of layers
+// may be repeated with the same weights.  config.json lists the layers one by one; the keys are this family's own.
+struct NizoraxConfig : ModelConfig {
+    struct Layer {
+        std::string type;                         // "attention" | "lightning"
+        int64_t heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+        // attention
+        double diff = 0, scale = 0, rot_base = 10000.0;
+        int64_t window = 0, rot_dims = 0;         // 0: no window / no rotation
+        bool rot_scaled = false;
+        double rot_factor = 1, rot_low = 1, rot_high = 1, rot_original = 1;
+        // lightning
+        std::vector<double> decay;                // a number per head
+        // feed-forward
+        std::string mlp;                          // "" (none) | "dense" | "moe"
+        int64_t ff = 0;                           // dense
+        int64_t experts = 0, top = 0, expert_ff = 0, shared_ff = 0, groups = 0, keep = 0;   // moe; groups 0: none; shared_ff 0: none
+        double route_scale = 1.0;
+    };
+    std::vector<Layer> layers;
+    double norm_eps = 1e-5, embedding_scale = 1.0, logit_scale = 1.0;
+    int64_t canon_taps = 0;                       // 0: no convolution on the sublayers' inputs
+    bool has_loop = false;
+    int64_t loop_start = 0, loop_stop = 0, loop_times = 1;
+
+    static NizoraxConfig from_json(const Json& d, const std::string& where);
+    Json to_json() const override;
+    // Layer indices in the order they run: those before the repeated run once, the run `times` times, the rest once.
+    std::vector<int> run_order() const;
+};
+
+ModelPlan nizorax_plan(const NizoraxConfig& cfg);
+
 // ------------------------------------------------------------------------------------ registry
 struct Architecture {
     std::string name;

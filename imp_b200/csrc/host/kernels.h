@@ -116,12 +116,19 @@ int imp_concat_streams(void* out, const float* h, const void* branch, const floa
                        int d, int act_dtype, void* stream);
 int imp_add_layernorm_ex(float* h, float h_mult, const void* branch, const float* col_scale, const void* w, const void* bias, void* out,
                          const int* rows, int n_out_rows, int d, float eps, int act_dtype, int w_dtype, int write_h, void* stream);
+int imp_add_normed_layernorm(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
+                             float eps, void* out, const int* rows, int n_out_rows, int d, int act_dtype, int w_dtype, int write_h,
+                             void* stream);
 // the general scan over a decaying matrix state and the kernels around it (delta_rule.cu)
 int imp_lsr_scan(int mode, const float* kw, const float* q, const float* w, const float* p, const float* z, const float* v,
                  const float* scal, const float* head_decay, float* state, float* out, const int* q_start, const int* slots,
                  int n_seqs, int D, int H, int Dv, void* stream);
 int imp_retention_prepare(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, float* q, float* kw, float* v,
                           float* scal, int act_dtype, void* stream);
+int imp_retention_prepare_ex(const void* proj, int64_t ld, int n_tokens, int H, int D, int Dv, float k_scale, int act, float* q, float* kw,
+                             float* v, float* scal, int act_dtype, void* stream);
+int imp_lsr_output_row(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, int gate_act, float eps, int n_tokens,
+                       int n, int act_dtype, void* stream);
 int imp_gdelta_prepare(const void* proj, int64_t ld, const float* dlog, const float* w0, const float* a_bias, float decay_scale,
                        float unit_eps, int n_tokens, int H, int D, float* q, float* kw, float* w, float* p, float* z, float* v,
                        float* scal, int act_dtype, void* stream);
@@ -137,12 +144,23 @@ int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv,
                     const int* positions, const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* q_out,
                     int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype, int* status,
                     void* stream);
+int imp_qkv_prepare_ex(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
+                       const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, int pairing, int v_share,
+                       const float* head_mult, const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
+                       int n_seqs, void* q_out, int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype,
+                       int* status, void* stream);
+int imp_diff_combine(void* y, const void* attn, int64_t ld, int n_tokens, int G, int R, int Dc, int Dv, const float* lambda, float eps,
+                     float out_scale, int dtype, void* stream);
 int imp_head_gate(void* y, int64_t y_ld, const void* g, int64_t g_ld, int n_tokens, int H, int Dv, int dtype, void* stream);
 int imp_rms_pair_mean(void* out, const void* a, const float* wa, float ca, const void* b, const float* wb, float cb, int n_rows, int d,
                       float eps, int dtype, void* stream);
 int imp_gated_act(void* out, const void* gate_up, int n_tokens, int F, int block, int act, int dtype, void* stream);
 int imp_act_rows(void* out, const void* x, int64_t ld, int n_tokens, int n, int act, int dtype, void* stream);
 int imp_gather_head_cols(void* dst, const void* src, int n_tokens, int H, int ds, int n, int dtype, void* stream);
+// a short causal convolution added to its input; a normalised polynomial as activation (short_conv.cu)
+int imp_add_conv(void* out, const void* x, int64_t ld, const float* w, int taps, float* state, const int* seq_of_token, const int* q_start,
+                 const int* slots, int n_tokens, int n_seqs, int C, int shift_state, int dtype, int* status, void* stream);
+int imp_polynorm(void* out, const void* z, int64_t ld, int n_tokens, int n, const float* coef, float eps, int dtype, void* stream);
 // products over groups: per-head matrices, routed experts (grouped_gemm.cu)
 int imp_grouped_gemm(void* C, int64_t ldc, int64_t c_group_cols, const void* A, int64_t lda, int64_t a_group_cols,
                      const int* a_rows, const void* W, const void* W2, int64_t w_group_stride, int64_t ldw, const int* seg,
@@ -171,6 +189,8 @@ int imp_wkv_output(void* y, const float* o, const void* g, int64_t ldg, const fl
 // routed experts (moe.cu)
 int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
                   int* idx, float* wts, float* gate, int act_dtype, void* stream);
+int imp_moe_route_ex(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                     int* idx, float* wts, float* gate, int score_mode, int n_groups, int keep, float weight_scale, int act_dtype, void* stream);
 int imp_moe_sort(const int* idx, int n_tokens, int top, int E, int* seg, int* row_token, int* pair_row, void* stream);
 int imp_gather_rows(void* dst, const void* src, int64_t ld, const int* idx, int n_rows, int d, int dtype, void* stream);
 int imp_moe_combine(void* out, const void* y, const int* pair_row, const float* wts, int n_tokens, int top, const void* shared,

@@ -166,6 +166,13 @@ Tensor summed(Runtime& rt, const Branch& b) {
         check_launch(imp_gemm_bf16_tc_swap_sum(b.t.data, b.t.stride0, epi, b.parts, (int)rows(b.t), (int)cols(b.t), b.n_splits, rt.stream),
                      "gemm_bf16_tc_swap_sum");
     }
+    if (b.own_norm.weight && !b.empty()) {
+        need(contiguous(b.t), "summed: a branch with a norm of its own must be dense");
+        ++rt.launches;
+        check_launch(imp_add_normed_layernorm(nullptr, b.t.data, b.own_norm.weight, b.own_norm.bias, b.own_norm.eps, nullptr, nullptr, 0.f, b.t.data, nullptr,
+                                              (int)rows(b.t), (int)cols(b.t), b.t.dtype, b.own_norm.dtype, 0, rt.stream),
+                     "add_normed_layernorm");
+    }
     if (b.col_scale && !b.empty()) {
         ++rt.launches;
         check_launch(imp_scale_columns(b.t.data, b.t.stride0, (int)rows(b.t), (int)cols(b.t), b.col_scale, b.t.dtype, rt.stream), "scale_columns");

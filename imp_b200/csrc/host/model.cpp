@@ -88,16 +88,36 @@ void Diagnostics::dump_stream(Step& st, int run, const Tensor& h, const Branch& 
         IMP_CUDA(cudaMemcpyAsync(raw.data(), pending.t.data, raw.size(), cudaMemcpyDeviceToHost, st.rt->stream));
         if (pending.col_scale) IMP_CUDA(cudaMemcpyAsync(scale.data(), pending.col_scale, d * 4, cudaMemcpyDeviceToHost, st.rt->stream));
         IMP_CUDA(cudaStreamSynchronize(st.rt->stream));
-        for (size_t i = 0; i < n; ++i) {
+        auto widen = [](const std::vector<char>& bytes, int dtype, size_t i) {
             float v;
-            if (pending.t.dtype == F32) {
-                v = ((const float*)raw.data())[i];
+            if (dtype == F32) {
+                v = ((const float*)bytes.data())[i];
             } else {
-                const uint32_t bits = (uint32_t)((const uint16_t*)raw.data())[i] << 16;
+                const uint32_t bits = (uint32_t)((const uint16_t*)bytes.data())[i] << 16;
                 memcpy(&v, &bits, 4);
             }
-            hs[i] += scale[i % d] * v;
+            return v;
+        };
+        std::vector<double> pv(n);
+        for (size_t i = 0; i < n; ++i) pv[i] = widen(raw, pending.t.dtype, i);
+        if (pending.own_norm.weight) {
+            // the branch's own layer norm, row by row
+            const BranchNorm& bn = pending.own_norm;
+            std::vector<char> wb(d * elem_size(bn.dtype)), bb(d * elem_size(bn.dtype));
+            IMP_CUDA(cudaMemcpyAsync(wb.data(), bn.weight, wb.size(), cudaMemcpyDeviceToHost, st.rt->stream));
+            if (bn.bias) IMP_CUDA(cudaMemcpyAsync(bb.data(), bn.bias, bb.size(), cudaMemcpyDeviceToHost, st.rt->stream));
+            IMP_CUDA(cudaStreamSynchronize(st.rt->stream));
+            for (size_t r = 0; r < n / d; ++r) {
+                double mean = 0, var = 0;
+                for (size_t c = 0; c < d; ++c) mean += pv[r * d + c];
+                mean /= (double)d;
+                for (size_t c = 0; c < d; ++c) var += (pv[r * d + c] - mean) * (pv[r * d + c] - mean);
+                const double inv = 1.0 / std::sqrt(var / (double)d + (double)bn.eps);
+                for (size_t c = 0; c < d; ++c)
+                    pv[r * d + c] = (pv[r * d + c] - mean) * inv * widen(wb, bn.dtype, c) + (bn.bias ? widen(bb, bn.dtype, c) : 0.f);
+            }
         }
+        for (size_t i = 0; i < n; ++i) hs[i] += (float)(scale[i % d] * pv[i]);
     }
     const std::string path = dump_dir + "/step" + std::to_string(dump_step_) + "_run" + std::to_string(run) + ".f32";
     if (FILE* f = fopen(path.c_str(), "wb")) {
@@ -314,7 +334,14 @@ void DeviceModel::finish_build() {
         const bool next_takes = j + 1 < order_.size() ? blocks_[(size_t)order_[j + 1]]->takes_column_scale() : final_norm_->takes_column_scale();
         scale_ok[(size_t)order_[j]] = scale_ok[(size_t)order_[j]] && next_takes;
     }
+    // And for one that carries a norm of its own.
+    std::vector<bool> norm_ok(blocks_.size(), true);
+    for (size_t j = 0; j < order_.size(); ++j) {
+        const bool next_takes = j + 1 < order_.size() ? blocks_[(size_t)order_[j + 1]]->takes_normed_branch() : final_norm_->takes_normed_branch();
+        norm_ok[(size_t)order_[j]] = norm_ok[(size_t)order_[j]] && next_takes;
+    }
     for (size_t i = 0; i < blocks_.size(); ++i) {
+        blocks_[i]->norm_pending = norm_ok[i];
         blocks_[i]->scale_pending = scale_ok[i];
         keep_embedding_ = keep_embedding_ || blocks_[i]->wants_embedding();
     }

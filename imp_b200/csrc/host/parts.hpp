@@ -114,12 +114,21 @@ void stage(Step& st, const char* name, const Branch& b);   // an unsummed branch
 // A branch output: nothing, a tensor, or the unsummed parts of one ([n_splits, M, N] float32 whose
 // sum in split order, rounded to `t`'s type, is the value that belongs into `t`).  With `col_scale` the
 // branch stands for that tensor times a 32-bit factor per column: whoever adds it into the stream multiplies in
-// 32-bit while adding (a norm that says takes_column_scale()), and summed() applies it for everyone else.
+// 32-bit while adding (a norm that says takes_column_scale()), and summed() applies it for everyone else.  With `own_norm`
+// the branch stands for the layer norm of that tensor (a norm of the branch's own, applied before it joins the stream): a norm
+// that says takes_normed_branch() normalises it while adding, summed() does it for everyone else.
+struct BranchNorm {
+    const void* weight = nullptr;   // [cols]; null: the branch has no norm of its own
+    const void* bias = nullptr;     // [cols] or null
+    float eps = 0.f;
+    int dtype = F32;                // of weight and bias
+};
 struct Branch {
     Tensor t{};
     float* parts = nullptr;
     int n_splits = 0;
     const float* col_scale = nullptr;   // float32 [cols], or null
+    BranchNorm own_norm{};
     bool empty() const { return t.data == nullptr; }
     bool split() const { return parts != nullptr; }
     static Branch of(const Tensor& t) { Branch b; b.t = t; return b; }
@@ -138,6 +147,9 @@ struct Norm : Part {
     const char* category() const override { return "norm"; }
     virtual bool takes_split_sum() const { return false; }
     virtual bool takes_column_scale() const { return false; }   // multiplies a branch's col_scale in while adding
+    virtual bool takes_normed_branch() const { return false; }  // applies a branch's own_norm while adding
+    // This norm as the own norm of a branch (a layer norm's weight, bias and eps); false: it cannot ride with a branch.
+    virtual bool as_branch_norm(BranchNorm* out) const { (void)out; return false; }
     virtual Tensor add_norm(Step& st, Tensor h, const Branch& branch, const int32_t* rows = nullptr, int n_rows = 0) = 0;
     // Post-norm: h <- norm(h_mult * h + branch), the normalised sum stored as the stream (32-bit); returns its copy in
     // the activation type.  Only norms that say stores_stream() implement it.
@@ -179,6 +191,8 @@ struct Block : Part {
     virtual bool takes_split_sum() const { return false; }   // the pending it is given may be unsummed
     bool scale_pending = false;                          // set by the model: the pending it returns may carry a col_scale
     virtual bool takes_column_scale() const { return false; }   // the pending it is given may carry a col_scale
+    bool norm_pending = false;                           // set by the model: the pending it returns may carry a norm of its own
+    virtual bool takes_normed_branch() const { return false; }  // the pending it is given may carry a norm of its own
     virtual bool wants_embedding() const { return false; }      // reads Step::embedding_out
     virtual Mixer* mixer() const { return nullptr; }     // the part that owns this layer's cache, if any
     // A block with several mixers names them in the order of its mixer slots; each owns a cache, and forward()
@@ -253,6 +267,7 @@ std::vector<std::string> known_parts(const std::string& category);
 void ensure_builtin_parts();   // registers the library's own kinds once
 void register_mixer_parts();    // parts_mixers.cpp: the kinds beyond plain attention (called by ensure_builtin_parts)
 void register_recurrent_parts();   // parts_recurrent.cpp: retention, the delta rules over the general scan, attention with gated heads, the post-norm block
+void register_sandwich_parts();    // parts_sandwich.cpp: the block with a norm before and after each sublayer, the short convolution on a sublayer's input, differential attention, the polynomial feed-forward
 void register_routed_parts();   // parts_routed.cpp: layer norm, latent attention, wkv, routed experts, blocks with scaled branches
 
 // Builds parts and owns them.  Parts without tensors are shared between equal specs.

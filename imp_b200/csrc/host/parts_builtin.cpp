@@ -359,6 +359,7 @@ void ensure_builtin_parts() {
         register_part_class("head", "linear_head", simple_class<LinearHead>(&LinearHead::specs), true);
         register_mixer_parts();
         register_routed_parts();
+        register_sandwich_parts();
         register_recurrent_parts();
     });
 }

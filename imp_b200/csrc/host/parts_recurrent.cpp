@@ -77,12 +77,18 @@ CacheSpec scan_state(int64_t H, int64_t D, int64_t Dv) {
 // Linear attention with a fixed decay per head and neither softmax nor denominator:
 //   q, k [H heads of D], v [H heads of Dv] = W x; k times key_scale;  S <- decay_h S + k v^T;  o = S^T q
 //   y = o / rms(o) per head (no weight) * silu(W_g x);  out = W_o y.
+// Options: an activation on q, k and v (`qkv_act`: "none" | "silu"); the gate's activation (`gate_act`: "silu" | "sigmoid"); the
+// read-out normalised per head or over all heads together (`norm_over`: "head" | "row"); a weight on the normalised
+// read-out (`out_norm`: a tensor [H * Dv]).
 // State per request: S (H heads of D x Dv, float32), zero at the start.
-// params: hidden_size, num_heads, key_dim, value_dim, decay (a number per head), key_scale (default key_dim^-1/2), norm_eps.
+// params: hidden_size, num_heads, key_dim, value_dim, decay (a number per head), key_scale (default key_dim^-1/2), norm_eps,
+//         qkv_act, gate_act, norm_over, out_norm.
 struct Retention : Mixer {
     int H, D, Dv;
     float eps, k_scale;
-    Tensor w_in, w_o, decay;
+    int qkv_act = 0, gate_act = 0;
+    bool norm_row = false;
+    Tensor w_in, w_o, decay, out_norm{};   // out_norm float32
 
     struct Sizes {
         int64_t d, H, D, Dv;
@@ -100,12 +106,18 @@ struct Retention : Mixer {
         s.emplace_back("k_proj", TensorSpec{{z.H * z.D, z.d}});
         s.emplace_back("v_proj", TensorSpec{{z.H * z.Dv, z.d}});
         s.emplace_back("gate_proj", TensorSpec{{z.H * z.Dv, z.d}});
+        if (p.get_bool("out_norm", false)) s.emplace_back("out_norm", TensorSpec{{z.H * z.Dv}, "norm", "one_plus_normal"});
         s.emplace_back("o_proj", TensorSpec{{z.d, z.H * z.Dv}});
         return s;
     }
     static CacheSpec cache(const Json& p) {
         const Sizes z = sizes(p);
         return scan_state(z.H, z.D, z.Dv);
+    }
+    static int one_of(const Json& p, const char* key, const char* first, const char* second) {
+        const std::string v = p.get_string(key, first);
+        if (v != first && v != second) fail(IMP_ERROR_INVALID_MODEL, std::string("retention: '") + key + "' is '" + v + "' (known: " + first + ", " + second + ")");
+        return v == second ? 1 : 0;
     }
     explicit Retention(BuildArgs& a) {
         const char* me = "retention";
@@ -120,10 +132,18 @@ struct Retention : Mixer {
             if (!e.is_number()) fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": 'decay' must list numbers");
             dec.push_back((float)e.as_double());
         }
+        qkv_act = one_of(a.params, "qkv_act", "none", "silu");
+        gate_act = one_of(a.params, "gate_act", "silu", "sigmoid");
+        norm_row = one_of(a.params, "norm_over", "head", "row") == 1;
         Runtime& rt = *a.rt;
         decay = upload_f32(rt, *a.store, dec);
         w_in = cat_rows_padded(rt, *a.store, {a.tensor("q_proj"), a.tensor("k_proj"), a.tensor("v_proj"), a.tensor("gate_proj")});
         w_o = a.tensor("o_proj");
+        if (a.params.get_bool("out_norm", false)) {
+            out_norm = to_float32(rt, *a.store, a.tensor("out_norm"));
+            IMP_CUDA(cudaStreamSynchronize(rt.stream));
+            a.drop("out_norm");
+        }
         for (const char* n : {"q_proj", "k_proj", "v_proj", "gate_proj"}) a.drop(n);
     }
     Branch forward(Step& st, Tensor x, LayerCache* cache) override {
@@ -134,13 +154,18 @@ struct Retention : Mixer {
         linear(rt, proj, x, w_in);
         ScanBuffers b(rt, T, H, D, Dv, false, false);
         rt.launches += 3;
-        check_launch(imp_retention_prepare(proj.data, proj.stride0, (int)T, H, D, Dv, k_scale, b.q, b.kw, b.v, b.scal, rt.dtype, rt.stream), "retention_prepare");
+        check_launch(imp_retention_prepare_ex(proj.data, proj.stride0, (int)T, H, D, Dv, k_scale, qkv_act, b.q, b.kw, b.v, b.scal, rt.dtype, rt.stream),
+                     "retention_prepare");
         check_launch(imp_lsr_scan(0, b.kw, b.q, nullptr, nullptr, nullptr, b.v, b.scal, (const float*)decay.data, (float*)cache->view.states[0].data, b.o,
                                   st.view.q_start, st.view.state_slots, st.B(), D, H, Dv, rt.stream),
                      "lsr_scan");
         Tensor y = rt.empty(T, (int64_t)H * Dv);
         const Tensor gate = col_slice(proj, (int64_t)2 * H * D + (int64_t)H * Dv, (int64_t)H * Dv);
-        check_launch(imp_gdr_output_ex(y.data, b.o, gate.data, gate.stride0, nullptr, 0, 0, eps, (int)T, H, Dv, rt.dtype, rt.stream), "gdr_output");
+        const float* wn = out_norm.data ? (const float*)out_norm.data : nullptr;
+        if (norm_row)
+            check_launch(imp_lsr_output_row(y.data, b.o, gate.data, gate.stride0, wn, gate_act, eps, (int)T, H * Dv, rt.dtype, rt.stream), "lsr_output_row");
+        else
+            check_launch(imp_gdr_output_ex(y.data, b.o, gate.data, gate.stride0, wn, wn ? Dv : 0, gate_act, eps, (int)T, H, Dv, rt.dtype, rt.stream), "gdr_output");
         return linear(rt, rt.empty(T, rows(w_o)), y, w_o, defer_out);
     }
 };

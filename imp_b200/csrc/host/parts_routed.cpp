@@ -27,8 +27,10 @@ Branch parts_summed(Runtime& rt, const Branch& b) {
     if (!b.split()) return b;
     Branch plain = b;
     plain.col_scale = nullptr;
+    plain.own_norm = BranchNorm{};
     Branch out = Branch::of(summed(rt, plain));
     out.col_scale = b.col_scale;
+    out.own_norm = b.own_norm;
     return out;
 }
 
@@ -46,13 +48,29 @@ struct LayerNorm : Norm {
         }
     }
     bool takes_column_scale() const override { return true; }
+    bool takes_normed_branch() const override { return true; }
+    bool as_branch_norm(BranchNorm* out) const override {
+        out->weight = weight.data;
+        out->bias = bias.data;
+        out->eps = eps;
+        out->dtype = weight.dtype;
+        return true;
+    }
     bool stores_stream() const override { return true; }
+    // A branch with a norm of its own that this kernel family cannot apply while adding (another weight type, or factors per
+    // column as well) gets it applied first.
+    Branch plain_or_normed(Runtime& rt, const Branch& branch) const {
+        Branch b = parts_summed(rt, branch);
+        if (b.own_norm.weight && (b.col_scale || b.own_norm.dtype != weight.dtype)) b = Branch::of(summed(rt, b));
+        return b;
+    }
     Tensor add_norm_store(Step& st, Tensor h, float h_mult, const Branch& branch) override {
         Runtime& rt = *st.rt;
         const int d = (int)cols(h);
         Tensor out = rt.empty(rows(h), d);
         if (h.dtype != F32 || !contiguous(h) || numel(weight) != d) fail(IMP_ERROR_INVALID_ARG, "layernorm: the stream must be dense float32 [T, d], the weight [d]");
-        const Branch b = parts_summed(rt, branch);
+        Branch b = parts_summed(rt, branch);
+        if (b.own_norm.weight) b = Branch::of(summed(rt, b));
         if (!b.empty() && (rows(b.t) != rows(h) || cols(b.t) != d || b.t.dtype != out.dtype || !contiguous(b.t)))
             fail(IMP_ERROR_INVALID_ARG, "layernorm: the branch must be dense, of the stream's shape and the output's type");
         ++rt.launches;
@@ -67,10 +85,17 @@ struct LayerNorm : Norm {
         const int d = (int)cols(h);
         Tensor out = rt.empty(n, d, -1, /*step=*/rows_idx != nullptr);
         if (h.dtype != F32 || !contiguous(h) || numel(weight) != d) fail(IMP_ERROR_INVALID_ARG, "layernorm: the stream must be dense float32 [T, d], the weight [d]");
-        const Branch b = parts_summed(rt, branch);
+        const Branch b = plain_or_normed(rt, branch);
         if (!b.empty() && (rows(b.t) != rows(h) || cols(b.t) != d || b.t.dtype != out.dtype || !contiguous(b.t)))
             fail(IMP_ERROR_INVALID_ARG, "layernorm: the branch must be dense, of the stream's shape and the output's type");
         ++rt.launches;
+        if (b.own_norm.weight) {
+            // the branch's own norm, the sum and this norm in one pass
+            check_launch(imp_add_normed_layernorm((float*)h.data, b.t.data, b.own_norm.weight, b.own_norm.bias, b.own_norm.eps, weight.data, bias.data, eps,
+                                                  out.data, rows_idx, (int)n, d, out.dtype, weight.dtype, rows_idx ? 0 : 1, rt.stream),
+                         "add_normed_layernorm");
+            return out;
+        }
         check_launch(imp_add_layernorm_ex((float*)h.data, 1.f, b.empty() ? nullptr : b.t.data, b.col_scale, weight.data, bias.data, out.data, rows_idx,
                                           (int)n, d, eps, out.dtype, weight.dtype, rows_idx ? 0 : 1, rt.stream),
                      "add_layernorm");
@@ -323,9 +348,18 @@ struct Wkv : Mixer {
 // The experts' matrices are stacked at load; a step sorts its (token, choice) pairs by expert on the device and runs two
 // products over the sorted list (csrc/grouped_gemm.cu), so its launches do not depend on the routing.
 //
-// params: hidden_size, num_experts, top_k, expert_size, shared_size (0: no shared expert).
+// Options: the router without a bias (`router_bias`: false); sigmoid scores, a chosen expert weighing its score times
+// `weight_scale`, not renormalised (`scores`: "sigmoid"; default "softmax" as above); experts in `num_groups` equal groups of
+// neighbours of which the `keep_groups` best (by the sum of a group's two largest scores) can be chosen from; a shared expert
+// that is added as it is (`shared_gate`: false).
+//
+// params: hidden_size, num_experts, top_k, expert_size, shared_size (0: no shared expert), router_bias, scores, weight_scale,
+//         num_groups, keep_groups, shared_gate.
 struct RoutedExperts : FeedForward {
     int64_t d, E, top, F, Fs;
+    bool has_bias = true, has_sgate = true;
+    int score_mode = 0, n_groups = 0, keep_groups = 0;
+    float weight_scale = 1.f;
     Tensor w_gate, w_up, w_down;       // [E * F, d], [E * F, d], [E * d, F]; or w_gate [E * 2F, d], gate and up rows alternating in runs of 8
     bool interleaved = false;
     Tensor router, router_bias, sg;    // float32
@@ -339,7 +373,13 @@ struct RoutedExperts : FeedForward {
         if (E <= 0 || top <= 0 || top > E || F <= 0 || Fs < 0) fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": 0 < top_k <= num_experts and positive sizes");
         TensorSpecs s;
         s.emplace_back("router", TensorSpec{{E, d}});
-        s.emplace_back("router_bias", TensorSpec{{E}, "vector", "normal"});
+        if (p.get_bool("router_bias", true)) s.emplace_back("router_bias", TensorSpec{{E}, "vector", "normal"});
+        const int64_t ng = p.get_int("num_groups", 0), keep = p.get_int("keep_groups", 0);
+        if (ng < 0 || (ng > 0 && (E % ng || keep <= 0 || keep > ng || top > keep * (E / ng))))
+            fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": " + std::to_string(ng) + " groups must divide the " + std::to_string(E) + " experts, and the " +
+                                              std::to_string(keep) + " kept groups must hold the " + std::to_string(top) + " chosen experts");
+        const std::string sc = p.get_string("scores", "softmax");
+        if (sc != "softmax" && sc != "sigmoid") fail(IMP_ERROR_INVALID_MODEL, std::string(me) + ": unknown scores '" + sc + "' (known: softmax, sigmoid)");
         for (int64_t e = 0; e < E; ++e) {
             const std::string n = std::to_string(e);
             s.emplace_back("gate_" + n, TensorSpec{{F, d}});
@@ -350,7 +390,7 @@ struct RoutedExperts : FeedForward {
             s.emplace_back("shared_gate", TensorSpec{{Fs, d}});
             s.emplace_back("shared_up", TensorSpec{{Fs, d}});
             s.emplace_back("shared_down", TensorSpec{{d, Fs}});
-            s.emplace_back("shared_mix", TensorSpec{{1, d}});
+            if (p.get_bool("shared_gate", true)) s.emplace_back("shared_mix", TensorSpec{{1, d}});
         }
         return s;
     }
@@ -359,6 +399,12 @@ struct RoutedExperts : FeedForward {
         const char* me = "routed_experts";
         d = need_int(a.params, "hidden_size", me), E = need_int(a.params, "num_experts", me), top = need_int(a.params, "top_k", me);
         F = need_int(a.params, "expert_size", me), Fs = a.params.get_int("shared_size", 0);
+        has_bias = a.params.get_bool("router_bias", true);
+        has_sgate = a.params.get_bool("shared_gate", true);
+        score_mode = a.params.get_string("scores", "softmax") == "sigmoid" ? 1 : 0;
+        weight_scale = (float)a.params.get_double("weight_scale", 1.0);
+        n_groups = (int)a.params.get_int("num_groups", 0);
+        keep_groups = (int)a.params.get_int("keep_groups", 0);
         Runtime& rt = *a.rt;
         std::vector<Tensor> gs, us, ds;
         for (int64_t e = 0; e < E; ++e) {
@@ -382,13 +428,13 @@ struct RoutedExperts : FeedForward {
         }
         w_down = cat_rows(rt, *a.store, ds);
         router = to_float32(rt, *a.store, a.tensor("router"));
-        router_bias = to_float32(rt, *a.store, a.tensor("router_bias"));
+        if (has_bias) router_bias = to_float32(rt, *a.store, a.tensor("router_bias"));
         if (Fs > 0) {
             Tensor gate = a.tensor("shared_gate"), up = a.tensor("shared_up");
             s_interleaved = Fs % SWIGLU_INTERLEAVE == 0 && gate.dtype == up.dtype;
             s_gu = s_interleaved ? interleave_gate_up(rt, *a.store, gate, up) : cat_rows(rt, *a.store, {gate, up});
             s_down = a.tensor("shared_down");
-            sg = to_float32(rt, *a.store, a.tensor("shared_mix"));
+            if (has_sgate) sg = to_float32(rt, *a.store, a.tensor("shared_mix"));
         }
         IMP_CUDA(cudaStreamSynchronize(rt.stream));
         for (int64_t e = 0; e < E; ++e) {
@@ -398,9 +444,11 @@ struct RoutedExperts : FeedForward {
             a.drop("down_" + n);
         }
         a.drop("router");
-        a.drop("router_bias");
-        if (Fs > 0)
-            for (const char* n : {"shared_gate", "shared_up", "shared_mix"}) a.drop(n);
+        if (has_bias) a.drop("router_bias");
+        if (Fs > 0) {
+            for (const char* n : {"shared_gate", "shared_up"}) a.drop(n);
+            if (has_sgate) a.drop("shared_mix");
+        }
     }
 
     Branch forward(Step& st, Tensor x) override {
@@ -414,8 +462,10 @@ struct RoutedExperts : FeedForward {
         int* row_token = rt.arena->take<int>((size_t)P);
         int* pair_row = rt.arena->take<int>((size_t)P);
         rt.launches += 5;
-        check_launch(imp_moe_route(x.data, x.stride0, (int)T, (int)d, (const float*)router.data, (const float*)router_bias.data, (int)E, (int)top,
-                                   Fs > 0 ? (const float*)sg.data : nullptr, idx, wts, gate, dt, rt.stream),
+        const bool gated = Fs > 0 && has_sgate;
+        check_launch(imp_moe_route_ex(x.data, x.stride0, (int)T, (int)d, (const float*)router.data, has_bias ? (const float*)router_bias.data : nullptr, (int)E,
+                                      (int)top, gated ? (const float*)sg.data : nullptr, idx, wts, gate, score_mode, n_groups, keep_groups, weight_scale, dt,
+                                      rt.stream),
                      "moe_route");
         check_launch(imp_moe_sort(idx, (int)T, (int)top, (int)E, seg, row_token, pair_row, rt.stream), "moe_sort");
         Tensor act = rt.empty(P, F);
@@ -469,7 +519,7 @@ struct RoutedExperts : FeedForward {
             linear(rt, shared, sa, s_down);
         }
         Tensor out = rt.empty(T, d);
-        check_launch(imp_moe_combine(out.data, y.data, pair_row, wts, (int)T, (int)top, Fs > 0 ? shared.data : nullptr, Fs > 0 ? gate : nullptr, (int)d,
+        check_launch(imp_moe_combine(out.data, y.data, pair_row, wts, (int)T, (int)top, Fs > 0 ? shared.data : nullptr, gated ? gate : nullptr, (int)d,
                                      dt, rt.stream),
                      "moe_combine");
         return Branch::of(out);

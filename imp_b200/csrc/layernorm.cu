@@ -276,3 +276,99 @@ IMP_API int imp_concat_streams(void* out, const float* h, const void* branch, co
     }
     return 0;
 }
+
+// A branch that is layer-normed before it joins the stream, and the stream's next norm, in one pass:
+//   n  = (branch - mean(branch)) / sqrt(var(branch) + eps_b) * bw + bb        (the branch's own norm)
+//   h  = h + n                                                                (stored when write_h)
+//   y  = (h - mean(h)) / sqrt(var(h) + eps) * w + b                           (the next norm; left out when w is null)
+// Without h the kernel is the branch's norm alone: out = n in the activation type.  One CTA per row; the branch row and the
+// sum wait in shared memory as 32-bit values between the passes, so every sum's order depends on the width alone.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(LN_BLOCK) add_normed_layernorm_kernel(float* __restrict__ h, const TA* __restrict__ branch, const TW* __restrict__ bw,
+                                                                        const TW* __restrict__ bb, float eps_b, const TW* __restrict__ w,
+                                                                        const TW* __restrict__ bias, float eps, TA* __restrict__ out,
+                                                                        const int* __restrict__ rows, int d, int write_h) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float ln_rows[];   // the branch row [d], then the sum [d]
+    __shared__ float scratch[33];
+    float* bs = ln_rows;
+    float* hs = ln_rows + d;
+    const int r = blockIdx.x;
+    const int64_t src = rows ? rows[r] : r;
+    const TA* brow = branch + src * d;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < d; i += LN_BLOCK) {
+        const float v = to_float(brow[i]);
+        bs[i] = v;
+        sum += v;
+    }
+    const float mean_b = block_sum(sum, scratch) / (float)d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += LN_BLOCK) {
+        const float c = bs[i] - mean_b;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv_b = rsqrtf(block_sum(ss, scratch) / (float)d + eps_b);
+    TA* orow = out ? out + (int64_t)r * d : nullptr;
+    if (!h) {
+        for (int i = threadIdx.x; i < d; i += LN_BLOCK)
+            orow[i] = from_float<TA>(fmaf((bs[i] - mean_b) * inv_b, to_float(bw[i]), bb ? to_float(bb[i]) : 0.f));
+        return;
+    }
+    float* hrow = h + src * d;
+    sum = 0.f;
+    for (int i = threadIdx.x; i < d; i += LN_BLOCK) {
+        const float v = hrow[i] + fmaf((bs[i] - mean_b) * inv_b, to_float(bw[i]), bb ? to_float(bb[i]) : 0.f);
+        if (write_h) hrow[i] = v;
+        hs[i] = v;
+        sum += v;
+    }
+    if (!w) return;
+    const float mean = block_sum(sum, scratch) / (float)d;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += LN_BLOCK) {
+        const float c = hs[i] - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += LN_BLOCK)
+        orow[i] = from_float<TA>(fmaf((hs[i] - mean) * inv, to_float(w[i]), bias ? to_float(bias[i]) : 0.f));
+}
+
+template <typename TA, typename TW>
+static cudaError_t launch_normed_layernorm(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
+                                           float eps, void* out, const int* rows, int n, int d, int write_h, cudaStream_t s) {
+    const size_t smem = (size_t)2 * d * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_normed_layernorm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return imp_launch(add_normed_layernorm_kernel<TA, TW>, dim3(n), dim3(LN_BLOCK), smem, s, h, (const TA*)branch, (const TW*)bw, (const TW*)bb, eps_b,
+                      (const TW*)w, (const TW*)bias, eps, (TA*)out, rows, d, write_h);
+}
+
+// h: [*, d] float32 stream or null (then out = the branch's norm alone); branch: dense [*, d] of the activation type with its
+// own norm (bw, optional bb, eps_b); w, bias, eps: the norm of the sum, w null to only add; rows: optional gather list (then
+// write_h must be 0).  All weights of one type.
+IMP_API int imp_add_normed_layernorm(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
+                                     float eps, void* out, const int* rows, int n_out_rows, int d, int act_dtype, int w_dtype, int write_h,
+                                     void* stream) {
+    if (n_out_rows == 0) return 0;
+    IMP_CHECK_ARG(branch && bw && d > 0 && n_out_rows > 0 && (h || out) && (out || !w) && (h || !rows), "imp_add_normed_layernorm: bad argument");
+    IMP_CHECK_ARG(!(rows && write_h), "imp_add_normed_layernorm: a gather list and write_h exclude each other");
+    IMP_CHECK_ARG((size_t)2 * d * sizeof(float) <= 200 * 1024, "imp_add_normed_layernorm: rows of %d values do not fit", d);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (act_dtype == IMP_F32)
+        e = w_dtype == IMP_F32 ? launch_normed_layernorm<float, float>(h, branch, bw, bb, eps_b, w, bias, eps, out, rows, n_out_rows, d, write_h, s)
+                               : launch_normed_layernorm<float, __nv_bfloat16>(h, branch, bw, bb, eps_b, w, bias, eps, out, rows, n_out_rows, d, write_h, s);
+    else
+        e = w_dtype == IMP_F32 ? launch_normed_layernorm<__nv_bfloat16, float>(h, branch, bw, bb, eps_b, w, bias, eps, out, rows, n_out_rows, d, write_h, s)
+                               : launch_normed_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, bw, bb, eps_b, w, bias, eps, out, rows, n_out_rows, d, write_h, s);
+    if (e != cudaSuccess) {
+        imp_set_error("imp_add_normed_layernorm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}

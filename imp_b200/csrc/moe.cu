@@ -2,7 +2,9 @@
 //
 //   z[t, e]   = x[t] . Wr[e] + b[e]                       32-bit
 //   chosen    = the `top` experts with the largest z (the lower index wins a tie)
-//   weight    = softmax over the chosen logits only
+//   weight    = softmax over the chosen logits only; or, with sigmoid scores s = sigmoid(z): weight = s * weight_scale
+//   groups    = optionally the experts form n_groups equal groups of neighbours; a group's score is the sum of its two
+//               largest scores, and only the experts of the `keep` best groups can be chosen
 //   gate[t]   = sigmoid(x[t] . Wg)                         one number per token, for a shared expert (optional)
 //   out[t]    = sum_k weight[t, k] * y[place(t, k)] + gate[t] * shared[t]
 //
@@ -43,13 +45,15 @@ template <typename TA, int TPB>
 __global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __restrict__ x, int64_t ldx, int n_tokens, int d,
                                                                const float* __restrict__ wr, const float* __restrict__ br, int E, int top,
                                                                const float* __restrict__ wg, int* __restrict__ idx, float* __restrict__ wts,
-                                                               float* __restrict__ gate, int vec) {
+                                                               float* __restrict__ gate, int vec, int score_mode, int n_groups, int keep,
+                                                               float weight_scale) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ __align__(16) float sm[];   // x [TPB][d4], then z [TPB][E]
+    extern __shared__ __align__(16) float sm[];   // x [TPB][d4], then z [TPB][E], then the groups' scores [TPB][n_groups]
     const int d4 = (d + 3) & ~3;
     float* xs = sm;
     float* z = sm + (size_t)TPB * d4;
+    float* gsc = z + (size_t)TPB * E;
     const int t0 = blockIdx.x * TPB, nt = min(TPB, n_tokens - t0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int e = tid; e < TPB * d4; e += ROUTE_BLOCK) {
@@ -86,8 +90,12 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __rest
         for (int tk = 0; tk < TPB; ++tk) {
             const float sum = warp_sum(acc[tk]);
             if (lane == 0 && tk < nt) {
-                if (e < E) z[tk * E + e] = sum + (br ? br[e] : 0.f);
-                else gate[t0 + tk] = 1.f / (1.f + expf(-sum));
+                if (e < E) {
+                    const float logit = sum + (br ? br[e] : 0.f);
+                    z[tk * E + e] = score_mode == 1 ? 1.f / (1.f + expf(-logit)) : logit;
+                } else {
+                    gate[t0 + tk] = 1.f / (1.f + expf(-sum));
+                }
             }
         }
     }
@@ -97,6 +105,41 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __rest
         float* zt = z + tk * E;
         const int64_t t = t0 + tk;
         float chosen[ROUTE_MAX_TOP];
+        if (n_groups > 0) {
+            // a group's score: the sum of its two largest scores (of its one score where a group is one expert); then `keep`
+            // rounds of arg-max over the groups, the lower index winning a tie; the experts of the other groups leave
+            float* gt = gsc + tk * n_groups;
+            const int per = E / n_groups;
+            for (int g = lane; g < n_groups; g += 32) {
+                float a = -INFINITY, b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    const float v = zt[e];
+                    if (v > a) b = a, a = v;
+                    else if (v > b) b = v;
+                }
+                gt[g] = per > 1 ? a + b : a;
+            }
+            __syncwarp();
+            for (int k = 0; k < keep; ++k) {
+                float best = -INFINITY;
+                int at = 0x7fffffff;
+                for (int g = lane; g < n_groups; g += 32) {
+                    const float v = gt[g];
+                    if (v > best) best = v, at = g;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
+                }
+                if (lane == 0 && at < n_groups) gt[at] = -INFINITY;   // kept
+                __syncwarp();
+            }
+            for (int e = lane; e < E; e += 32)
+                if (gt[e / per] != -INFINITY) zt[e] = -INFINITY;
+            __syncwarp();
+        }
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
             int at = 0x7fffffff;
@@ -117,7 +160,9 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) moe_route_kernel(const TA* __rest
             }
             __syncwarp();
         }
-        if (lane == 0) {
+        if (lane == 0 && score_mode == 1) {
+            for (int k = 0; k < top; ++k) wts[t * top + k] = chosen[k] * weight_scale;   // the scores themselves, not renormalised
+        } else if (lane == 0) {
             const float largest = chosen[0];   // the first chosen is the largest
             float sum = 0.f;
             for (int k = 0; k < top; ++k) {
@@ -242,49 +287,62 @@ IMP_API int imp_gather_rows(void* dst, const void* src, int64_t ld, const int* i
 
 template <typename TA, int TPB>
 static cudaError_t launch_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
-                                int* idx, float* wts, float* gate, int vec, size_t smem, cudaStream_t s) {
+                                int* idx, float* wts, float* gate, int vec, int score_mode, int n_groups, int keep, float weight_scale, size_t smem,
+                                cudaStream_t s) {
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<TA, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     return imp_launch(moe_route_kernel<TA, TPB>, dim3((n_tokens + TPB - 1) / TPB), dim3(ROUTE_BLOCK), smem, s, (const TA*)x, ldx, n_tokens, d, wr, br,
-                      E, top, wg, idx, wts, gate, vec);
+                      E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale);
 }
 
 template <typename TA>
 static cudaError_t route_by_size(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
-                                 int* idx, float* wts, float* gate, int vec, cudaStream_t s) {
+                                 int* idx, float* wts, float* gate, int vec, int score_mode, int n_groups, int keep, float weight_scale,
+                                 cudaStream_t s) {
     // more tokens a CTA where there are many (a row of the router is read once per CTA), one where there are few (more CTAs)
     int tpb = n_tokens >= 1024 ? 8 : n_tokens >= 256 ? 4 : n_tokens >= 64 ? 2 : 1;
     const int d4 = (d + 3) & ~3;
-    auto bytes = [&](int t) { return ((size_t)t * d4 + (size_t)t * E) * 4; };
+    auto bytes = [&](int t) { return ((size_t)t * d4 + (size_t)t * E + (size_t)t * n_groups) * 4; };
     while (tpb > 1 && bytes(tpb) > 160 * 1024) tpb /= 2;
     if (bytes(tpb) > 200 * 1024) return cudaErrorInvalidValue;
     switch (tpb) {
-        case 8: return launch_route<TA, 8>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(8), s);
-        case 4: return launch_route<TA, 4>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(4), s);
-        case 2: return launch_route<TA, 2>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(2), s);
-        default: return launch_route<TA, 1>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, bytes(1), s);
+        case 8: return launch_route<TA, 8>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, bytes(8), s);
+        case 4: return launch_route<TA, 4>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, bytes(4), s);
+        case 2: return launch_route<TA, 2>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, bytes(2), s);
+        default: return launch_route<TA, 1>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, bytes(1), s);
     }
 }
 
 // x [T, d] (activation type, rows ldx apart); wr float32 [E, d], br float32 [E] or null; wg float32 [d] or null (then
 // gate is not written).  idx int32 [T, top], wts float32 [T, top], gate float32 [T].
-IMP_API int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
-                          int* idx, float* wts, float* gate, int act_dtype, void* stream) {
+// score_mode 0: weights are the softmax over the chosen logits; 1: scores are sigmoid(z) and a weight is its score times
+// weight_scale.  n_groups > 0: only experts of the `keep` best of n_groups equal groups of neighbours can be chosen.
+IMP_API int imp_moe_route_ex(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                             int* idx, float* wts, float* gate, int score_mode, int n_groups, int keep, float weight_scale, int act_dtype,
+                             void* stream) {
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(x && wr && idx && wts && d > 0 && (!wg || gate), "imp_moe_route: bad argument");
     IMP_CHECK_ARG(E > 0 && E <= ROUTE_MAX_E && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                   "imp_moe_route: %d experts (at most %d), %d chosen (at most %d and no more than there are)", E, ROUTE_MAX_E, top, ROUTE_MAX_TOP);
+    IMP_CHECK_ARG((score_mode == 0 || score_mode == 1) && n_groups >= 0 && (n_groups == 0 || (E % n_groups == 0 && keep > 0 && keep <= n_groups &&
+                                                                                             top <= keep * (E / n_groups))),
+                  "imp_moe_route: %d groups over %d experts, %d kept, %d chosen", n_groups, E, keep, top);
     const int vec = (d % 4 == 0 && (uintptr_t)wr % 16 == 0 && (!wg || (uintptr_t)wg % 16 == 0)) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e = act_dtype == IMP_F32 ? route_by_size<float>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, s)
-                                         : route_by_size<__nv_bfloat16>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, s);
+    cudaError_t e = act_dtype == IMP_F32 ? route_by_size<float>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, s)
+                                         : route_by_size<__nv_bfloat16>(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, vec, score_mode, n_groups, keep, weight_scale, s);
     if (e != cudaSuccess) {
         imp_set_error("imp_moe_route: %s (rows of %d values, %d experts)", cudaGetErrorString(e), d, E);
         return (int)e;
     }
     return 0;
+}
+
+IMP_API int imp_moe_route(const void* x, int64_t ldx, int n_tokens, int d, const float* wr, const float* br, int E, int top, const float* wg,
+                          int* idx, float* wts, float* gate, int act_dtype, void* stream) {
+    return imp_moe_route_ex(x, ldx, n_tokens, d, wr, br, E, top, wg, idx, wts, gate, 0, 0, 0, 1.f, act_dtype, stream);
 }
 
 IMP_API int imp_moe_sort(const int* idx, int n_tokens, int top, int E, int* seg, int* row_token, int* pair_row, void* stream) {

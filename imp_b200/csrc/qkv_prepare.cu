@@ -3,10 +3,12 @@
 // or gate their heads.
 //
 //   qkv_prepare      per token: q heads  -> RMS norm with a weight shared by the heads (optional), rotation of the
-//                    first `rot` entries (pairs i, i + rot/2), times a number per head (optional) -> q_out, padded
+//                    first `rot` entries (pairs i, i + rot/2, or neighbours 2i, 2i + 1), times a number per head (optional) -> q_out, padded
 //                    to the cache's head size; k heads -> norm, rotation -> K page; v heads -> divided by their
 //                    root mean square (optional) -> V page.  Key and value heads may have different sizes: the
-//                    cache's head size is the larger one, the rest of a row is zeros.
+//                    cache's head size is the larger one, the rest of a row is zeros.  With v_share = n, n neighbouring key
+//                    heads read one value head (the product holds Hkv / n of them) and each caches a copy of it.
+//   diff_combine     two softmax maps per head over the same values: o = a1 - lambda * a2, o / rms(o) * out_scale
 //   head_gate        y[t, h, :] *= sigmoid(g[t, h])
 //   rms_pair_mean    out = ca * a / rms(a) * wa + cb * b / rms(b) * wb   (two branch outputs, each normalised over the width)
 //   gated_act        out = act(gate) * up for gelu (tanh form) and silu over [gate | up] rows
@@ -25,7 +27,7 @@ constexpr int QP_MAX_D = 512;
 template <typename TA, int PER>
 __global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
     const TA* __restrict__ proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* __restrict__ q_norm_w,
-    const float* __restrict__ k_norm_w, float eps, int v_norm, const float* __restrict__ inv_freq, int rot,
+    const float* __restrict__ k_norm_w, float eps, int v_norm, const float* __restrict__ inv_freq, int rot, int pairing, int v_share,
     const float* __restrict__ head_mult, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int bt_stride, int n_seqs, TA* __restrict__ q_out, int64_t q_ld, TA* __restrict__ k_cache,
     TA* __restrict__ v_cache, int page_size, int num_pages, int* status) {
@@ -52,7 +54,7 @@ __global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
         const bool is_q = unit < Hq, is_v = unit >= Hq + Hkv;
         const int head = is_q ? unit : is_v ? unit - Hq - Hkv : unit - Hq;
         const int n = is_v ? Dv : D;
-        const TA* src = proj + t * ld + (is_q ? (int64_t)head * D : is_v ? (int64_t)Hq * D + (int64_t)Hkv * D + (int64_t)head * Dv
+        const TA* src = proj + t * ld + (is_q ? (int64_t)head * D : is_v ? (int64_t)Hq * D + (int64_t)Hkv * D + (int64_t)(head / v_share) * Dv
                                                                          : (int64_t)Hq * D + (int64_t)head * D);
         TA* dst;
         if (is_q) {
@@ -84,7 +86,18 @@ __global__ void __launch_bounds__(QP_BLOCK) qkv_prepare_kernel(
                 if (d < n) x[i] = x[i] * r * (nw ? nw[d] : 1.f);
             }
         }
-        if (!is_v && rot > 0) {
+        if (!is_v && rot > 0 && pairing == 1) {
+            // neighbours: entry 2i pairs with 2i + 1, which the next lane holds, at angle pos * inv_freq[i]
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + i * 32;
+                const float partner = __shfl_xor_sync(0xffffffffu, x[i], 1);
+                if (d < rot) {
+                    const float sn = sin_s[d >> 1], cs = cos_s[d >> 1];
+                    x[i] = (d & 1) ? x[i] * cs + partner * sn : x[i] * cs - partner * sn;
+                }
+            }
+        } else if (!is_v && rot > 0) {
             // entry d < rot/2 pairs with d + rot/2, which another lane holds: the head goes through shared memory once
             float* row = rot_s[warp];
 #pragma unroll
@@ -184,24 +197,61 @@ __global__ void act_rows_kernel(T* __restrict__ out, const T* __restrict__ x, in
     }
 }
 
-IMP_API int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
-                            const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, const float* head_mult,
-                            const int* positions, const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* q_out,
-                            int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype, int* status,
-                            void* stream) {
+
+// attn [T, ld] holds, per token, G groups x 2 maps x R query heads of Dc entries (the order the paged attention kernels
+// want: the R heads of a map of a group share that map's key head).  Head h = g * R + j of the result:
+//   o = a[g, 0, j] - lambda * a[g, 1, j] over the first Dv entries;  y[t, h, :] = o / sqrt(mean(o^2) + eps) * out_scale.
+// A warp per (token, head); the difference and the norm in 32-bit.
+template <typename TA>
+__global__ void diff_combine_kernel(TA* __restrict__ y, const TA* __restrict__ attn, int64_t ld, int n_tokens, int G, int R, int Dc, int Dv,
+                                    const float* __restrict__ lambda, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int H = G * R;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * H) return;
+    const int64_t t = item / H;
+    const int h = (int)(item - t * H), g = h / R, j = h - g * R;
+    const TA* a1 = attn + t * ld + ((int64_t)(g * 2) * R + j) * Dc;
+    const TA* a2 = a1 + (int64_t)R * Dc;
+    const float lam = lambda[0];
+    float o[QP_MAX_D / 32], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < QP_MAX_D / 32; ++i) {
+        const int d = lane + i * 32;
+        o[i] = d < Dv ? fmaf(-lam, to_float(a2[d]), to_float(a1[d])) : 0.f;
+        ss = fmaf(o[i], o[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)Dv + eps) * out_scale;
+    TA* dst = y + (t * H + h) * Dv;
+#pragma unroll
+    for (int i = 0; i < QP_MAX_D / 32; ++i) {
+        const int d = lane + i * 32;
+        if (d < Dv) dst[d] = from_float<TA>(o[i] * r);
+    }
+}
+
+IMP_API int imp_qkv_prepare_ex(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
+                               const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, int pairing, int v_share,
+                               const float* head_mult, const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
+                               int n_seqs, void* q_out, int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype,
+                               int* status, void* stream) {
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(proj && positions && seq_of_token && block_table && q_out, "imp_qkv_prepare: null pointer");
     IMP_CHECK_ARG(Hq > 0 && Hkv > 0 && D > 0 && Dv > 0 && Dc >= D && Dc >= Dv && Dc <= QP_MAX_D,
                   "imp_qkv_prepare: head sizes %d / %d must fit the cache's %d (at most %d)", D, Dv, Dc, QP_MAX_D);
     IMP_CHECK_ARG(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "imp_qkv_prepare: the rotated part must be even and within the head");
     IMP_CHECK_ARG((q_norm_w == nullptr) == (k_norm_w == nullptr), "imp_qkv_prepare: q and k are normalised together or not at all");
-    IMP_CHECK_ARG(ld >= (int64_t)(Hq + Hkv) * D + (int64_t)Hkv * Dv && q_ld >= (int64_t)Hq * Dc, "imp_qkv_prepare: rows too short");
+    IMP_CHECK_ARG((pairing == 0 || pairing == 1) && v_share > 0 && Hkv % v_share == 0, "imp_qkv_prepare: pairing is 0 (halves) or 1 (neighbours); v_share divides the key heads");
+    IMP_CHECK_ARG(ld >= (int64_t)(Hq + Hkv) * D + (int64_t)(Hkv / v_share) * Dv && q_ld >= (int64_t)Hq * Dc, "imp_qkv_prepare: rows too short");
     IMP_CHECK_ARG(page_size > 0 && num_pages > 0, "imp_qkv_prepare: bad cache geometry");
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((unsigned)n_tokens, (unsigned)((Hq + 2 * Hkv + QP_UNITS - 1) / QP_UNITS));
 #define QP_LAUNCH(TA, PER)                                                                                                                    \
     imp_launch(qkv_prepare_kernel<TA, PER>, grid, dim3(QP_BLOCK), 0, s, (const TA*)proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w, k_norm_w, eps, \
-               v_norm, inv_freq, rot, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (TA*)q_out, q_ld, (TA*)k_cache,     \
+               v_norm, inv_freq, rot, pairing, v_share, head_mult, positions, seq_of_token, block_table, bt_stride, n_seqs, (TA*)q_out, q_ld, (TA*)k_cache,     \
                (TA*)v_cache, page_size, num_pages, status)
 #define QP_LAUNCH_PER(TA)                       \
     do {                                        \
@@ -214,6 +264,33 @@ IMP_API int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, 
     else QP_LAUNCH_PER(__nv_bfloat16);
 #undef QP_LAUNCH_PER
 #undef QP_LAUNCH
+    IMP_RETURN_LAUNCH();
+}
+
+IMP_API int imp_qkv_prepare(const void* proj, int64_t ld, int n_tokens, int Hq, int Hkv, int D, int Dv, int Dc, const float* q_norm_w,
+                            const float* k_norm_w, float eps, int v_norm, const float* inv_freq, int rot, const float* head_mult,
+                            const int* positions, const int* seq_of_token, const int* block_table, int bt_stride, int n_seqs, void* q_out,
+                            int64_t q_ld, void* k_cache, void* v_cache, int page_size, int num_pages, int act_dtype, int* status,
+                            void* stream) {
+    return imp_qkv_prepare_ex(proj, ld, n_tokens, Hq, Hkv, D, Dv, Dc, q_norm_w, k_norm_w, eps, v_norm, inv_freq, rot, 0, 1, head_mult, positions,
+                              seq_of_token, block_table, bt_stride, n_seqs, q_out, q_ld, k_cache, v_cache, page_size, num_pages, act_dtype, status,
+                              stream);
+}
+
+// y [T, G * R * Dv] dense; attn rows `ld` apart; lambda: one float32 on the device.
+IMP_API int imp_diff_combine(void* y, const void* attn, int64_t ld, int n_tokens, int G, int R, int Dc, int Dv, const float* lambda, float eps,
+                             float out_scale, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(y && attn && lambda && G > 0 && R > 0 && Dv > 0 && Dv <= Dc && Dc <= QP_MAX_D && ld >= (int64_t)2 * G * R * Dc,
+                  "imp_diff_combine: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t items = (int64_t)n_tokens * G * R;
+    const dim3 grid((unsigned)((items + 7) / 8));
+    if (dtype == IMP_F32)
+        imp_launch(diff_combine_kernel<float>, grid, dim3(256), 0, s, (float*)y, (const float*)attn, ld, n_tokens, G, R, Dc, Dv, lambda, eps, out_scale);
+    else
+        imp_launch(diff_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)y, (const __nv_bfloat16*)attn, ld, n_tokens, G, R, Dc, Dv,
+                   lambda, eps, out_scale);
     IMP_RETURN_LAUNCH();
 }
 

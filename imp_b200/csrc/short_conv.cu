@@ -1,0 +1,103 @@
+// A short causal convolution over time on each channel, added to its own input, and a normalised polynomial as
+// activation.
+//
+//   add_conv    out[t, c] = x[t, c] + sum_j w[c, j] * x[t - taps + 1 + j, c]   (j < taps; the last tap is the token itself)
+//               Tokens before the step's portion come from the request's state, which holds its last taps - 1 inputs
+//               ([slot][taps - 1][C] float32, the newest last, zeros at a request's start).  In a step of single tokens the
+//               kernel also shifts the state; otherwise imp_gdr_conv_state follows (it must not run before every token of
+//               the portion has read the old state).
+//   polynorm    out[t, :] = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e, powers element by element,
+//               rms(u) = sqrt(mean(u^2) + eps) over the row; the three sums and the result in 32-bit.
+#include "common.cuh"
+
+namespace {
+
+constexpr int SC_BLOCK = 256;
+constexpr int SC_MAX_TAPS = 64;
+
+template <typename TA>
+__global__ void __launch_bounds__(SC_BLOCK) add_conv_kernel(TA* __restrict__ out, const TA* __restrict__ x, int64_t ld, const float* __restrict__ w,
+                                                            int taps, float* __restrict__ state, const int* __restrict__ seq_of_token,
+                                                            const int* __restrict__ q_start, const int* __restrict__ slots, int n_seqs, int C,
+                                                            int shift_state, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    if (seq < 0 || seq >= n_seqs) {
+        if (threadIdx.x == 0) imp_report(status, IMP_BAD_SEQUENCE);
+        return;
+    }
+    const int start = q_start[seq];
+    const int lt = (int)t - start;                       // the token's place in its portion
+    float* st = state + (int64_t)slots[seq] * (taps - 1) * C;
+    for (int c = blockIdx.y * SC_BLOCK + threadIdx.x; c < C; c += gridDim.y * SC_BLOCK) {
+        const float own = to_float(x[t * ld + c]);
+        float acc = own;
+        for (int j = 0; j < taps; ++j) {
+            const int s = lt - (taps - 1) + j;           // which input, counted from the portion's first token
+            const float v = s >= 0 ? (j == taps - 1 ? own : to_float(x[(int64_t)(start + s) * ld + c])) : st[(int64_t)(taps - 1 + s) * C + c];
+            acc = fmaf(w[(int64_t)c * taps + j], v, acc);
+        }
+        out[t * (int64_t)C + c] = from_float<TA>(acc);
+        if (shift_state) {                               // one token a sequence: this thread alone reads and writes its channel
+            for (int i = 0; i + 1 < taps - 1; ++i) st[(int64_t)i * C + c] = st[(int64_t)(i + 1) * C + c];
+            if (taps > 1) st[(int64_t)(taps - 2) * C + c] = own;
+        }
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(SC_BLOCK) polynorm_kernel(TA* __restrict__ out, const TA* __restrict__ z, int64_t ld, int n, const float* __restrict__ coef,
+                                                            float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int64_t t = blockIdx.x;
+    const TA* row = z + t * ld;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < n; i += SC_BLOCK) {
+        const float v = to_float(row[i]), v2 = v * v;
+        s2 += v2;
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v2 * v2, v2, s6);
+    }
+    const float a = coef[0] * rsqrtf(block_sum(s2, scratch) / (float)n + eps);
+    const float b = coef[1] * rsqrtf(block_sum(s4, scratch) / (float)n + eps);
+    const float c = coef[2] * rsqrtf(block_sum(s6, scratch) / (float)n + eps);
+    const float e = coef[3];
+    TA* orow = out + t * (int64_t)n;
+    for (int i = threadIdx.x; i < n; i += SC_BLOCK) {
+        const float v = to_float(row[i]);
+        orow[i] = from_float<TA>(fmaf(v, fmaf(v, fmaf(v, c, b), a), e));    // a v + b v^2 + c v^3 + e
+    }
+}
+
+}  // namespace
+
+// x [T, ld] and out [T, C] dense, of the activation type; w float32 [C, taps]; state float32 [slots][taps - 1][C].
+IMP_API int imp_add_conv(void* out, const void* x, int64_t ld, const float* w, int taps, float* state, const int* seq_of_token, const int* q_start,
+                         const int* slots, int n_tokens, int n_seqs, int C, int shift_state, int dtype, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(out && x && w && seq_of_token && q_start && slots && C > 0 && ld >= C, "imp_add_conv: bad argument");
+    IMP_CHECK_ARG(taps >= 1 && taps <= SC_MAX_TAPS && (taps == 1 || state), "imp_add_conv: 1 to %d taps, and a state where there is more than one", SC_MAX_TAPS);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((unsigned)n_tokens, (unsigned)std::min((C + SC_BLOCK - 1) / SC_BLOCK, 64));
+    if (dtype == IMP_F32)
+        imp_launch(add_conv_kernel<float>, grid, dim3(SC_BLOCK), 0, s, (float*)out, (const float*)x, ld, w, taps, state, seq_of_token, q_start, slots,
+                   n_seqs, C, shift_state, status);
+    else
+        imp_launch(add_conv_kernel<__nv_bfloat16>, grid, dim3(SC_BLOCK), 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, ld, w, taps, state,
+                   seq_of_token, q_start, slots, n_seqs, C, shift_state, status);
+    IMP_RETURN_LAUNCH();
+}
+
+// z [T, ld], out [T, n] dense, of the activation type; coef float32 [4] = (a, b, c, e).
+IMP_API int imp_polynorm(void* out, const void* z, int64_t ld, int n_tokens, int n, const float* coef, float eps, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    IMP_CHECK_ARG(out && z && coef && n > 0 && ld >= n, "imp_polynorm: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IMP_F32) imp_launch(polynorm_kernel<float>, dim3(n_tokens), dim3(SC_BLOCK), 0, s, (float*)out, (const float*)z, ld, n, coef, eps);
+    else imp_launch(polynorm_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(SC_BLOCK), 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)z, ld, n, coef, eps);
+    IMP_RETURN_LAUNCH();
+}
