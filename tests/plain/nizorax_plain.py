@@ -186,8 +186,37 @@ def route(u, W, p, c):
     return idx, w, s
 
 
-def moe(u, W, p, c):
+def route_margin(u, W, p, c):
+    """Per token, the smallest gap a choice hangs on: between the last kept and the first dropped group, and between the
+    last chosen and the first refused score among the kept groups (infinite where nothing is refused)."""
+    r = c["router"]
+    E, top = r["experts"], r["top"]
+    s = torch.sigmoid(u @ W[p + "router"].T)
+    inf = torch.full((u.shape[0],), float("inf"), dtype=u.dtype)
+    margin = inf.clone()
+    allowed = torch.ones_like(s, dtype=torch.bool)
+    groups = r.get("groups")
+    if groups:
+        n, keep = groups["count"], groups["keep"]
+        per = E // n
+        gscore = s.view(-1, n, per).topk(min(2, per), dim=-1).values.sum(dim=-1)
+        if keep < n:
+            val = gscore.topk(keep + 1, dim=-1).values
+            margin = torch.minimum(margin, val[:, keep - 1] - val[:, keep])
+        best = gscore.topk(keep, dim=-1).indices
+        gmask = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, best, True)
+        allowed = gmask[:, :, None].expand(-1, -1, per).reshape(-1, E)
+    masked = s.masked_fill(~allowed, float("-inf"))
+    if top < int(allowed[0].sum()):
+        val = masked.topk(top + 1, dim=-1).values
+        margin = torch.minimum(margin, val[:, top - 1] - val[:, top])
+    return margin
+
+
+def moe(u, W, p, c, margins=None):
     idx, w, _ = route(u, W, p, c)
+    if margins is not None:
+        margins.append(route_margin(u, W, p, c))
     out = torch.zeros(u.shape[0], W[p + "e0.down"].shape[0], dtype=u.dtype)
     for t in range(u.shape[0]):
         for j in range(idx.shape[1]):
@@ -206,11 +235,12 @@ def run_order(cfg):
     return list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + list(range(loop["stop"], L))
 
 
-def forward(ids, W, cfg, streams=None):
-    """ids: token ids of one sequence -> logits [T, vocab].  With `streams` (a list), the stream after every layer run."""
+def forward(ids, W, cfg, streams=None, margins=None):
+    """ids: token ids of one sequence -> logits [T, vocab].  With `streams` (a list), the stream after every layer run; with
+    `margins` (a list), every routed layer run's margins per token."""
     eps = cfg["norm"]["eps"]
     dtype = W["embed"].dtype
-    x = W["embed"][torch.as_tensor(ids, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = W["embed"][torch.as_tensor(ids, dtype=torch.long)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     has_conv = bool(cfg.get("canon"))
     for i in run_order(cfg):
         layer = cfg["layers"][i]
@@ -230,9 +260,9 @@ def forward(ids, W, cfg, streams=None):
             u = layer_norm(x, W[p + "norm2"], W[p + "norm2.b"], eps)
             if has_conv:
                 u = add_causal_conv(u, W[p + "canon2"])
-            f = dense_ff(u, W, p + "mlp.", eps) if mlp["kind"] == "dense" else moe(u, W, p + "mlp.", mlp)
+            f = dense_ff(u, W, p + "mlp.", eps) if mlp["kind"] == "dense" else moe(u, W, p + "mlp.", mlp, margins)
             x = x + layer_norm(f, W[p + "norm2b"], W[p + "norm2b.b"], eps)
         if streams is not None:
             streams.append(x.clone())
     x = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
-    return (x @ W["head"].T * cfg["logit_scale"]).to(dtype)
+    return (x @ W["head"].T * cfg.get("logit_scale", 1.0)).to(dtype)
