@@ -29,6 +29,7 @@ Other runs, each printing its own JSON line:
     python bench.py --arch kazedra [--layers N] [--batch B]    Kazedra beside Qwen3 at equal sizes: prefill and decode
     python bench.py --arch kuzipel [--layers N] [--batch B]    Kuzipel beside Kazedra and Qwen3 at equal sizes
     python bench.py --arch pemidra [--layers N] [--batch B]    Pemidra beside Kazedra and Qwen3 at equal sizes
+    python bench.py --arch nizorax [--layers N] [--batch B]    Nizorax beside Pemidra, Kuzipel and Qwen3 at equal sizes
     python bench.py --workload 14b                        8 prompts of 8,192 tokens in 2,048-token portions, 512 tokens at T=0.7
 (`--context` may exceed the configured 4096: the cache and the position table grow with it.)
 """
@@ -752,14 +753,35 @@ def pemidra_config(width, heads, kv_heads, ff, layers, vocab):
             "max_positions": 8192}
 
 
+def nizorax_config(width, heads, kv_heads, ff, layers, vocab):
+    """Layers cycle through differential attention (two maps of 64 entries a head over values of 128, a window of 1,024
+    positions, the whole of each map rotated with slowed long wavelengths) with the dense feed-forward of the models beside
+    it, the same attention with routed experts (16 in 4 groups of which 2 are kept, two chosen, a shared one: together the
+    dense inner size), and lightning (heads of 128 keys and 128 values: Pemidra's retention geometry) with the dense
+    feed-forward; four taps on every sublayer's input."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.5, "scale": 64 ** -0.5, "mask": {"size": 1024},
+            "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    n_lig = width // 128
+    lig = {"heads": n_lig, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 4.0 * h / max(n_lig - 1, 1)) for h in range(n_lig)]}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": ff // 3}}
+    kinds = [("attention", attn, dense), ("attention", attn, moe), ("lightning", lig, dense)]
+    lays = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": kinds[i % 3][2]} for i in range(layers)]
+    return {"architecture": "Nizorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+            "canon": {"taps": 4}, "layers": lays, "max_positions": 8192}
+
+
 def run_arch(args):
-    """Prefill and decode of Kazedra, Kuzipel or Pemidra beside the models the engine already had at equal sizes (random weights): a
+    """Prefill and decode of Kazedra, Kuzipel, Pemidra or Nizorax beside the models the engine already had at equal sizes (random weights): a
     2,048-token prompt whole and in 512-token portions, and decode steps of `--batch` sequences at context 2,048, device
     time between CUDA events."""
     if args.arch == "kuzipel":
         return run_arch_beside(args, "kuzipel", kuzipel_config)
     if args.arch == "pemidra":
         return run_arch_beside(args, "pemidra", pemidra_config)
+    if args.arch == "nizorax":
+        return run_arch_beside(args, "nizorax", nizorax_config, beside={"pemidra": pemidra_config, "kuzipel": kuzipel_config})
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
     if args.only in ("prefill", "decode"):
@@ -814,8 +836,10 @@ def run_arch(args):
     return 0
 
 
-def run_arch_beside(args, arch, config_of):
-    """`arch` (its configuration made by `config_of`) beside Kazedra and Qwen3 at equal width and inner size."""
+def run_arch_beside(args, arch, config_of, beside=None):
+    """`arch` (its configuration made by `config_of`) beside the models of `beside` (name -> configuration function; Kazedra
+    unless given) and Qwen3 at equal width and inner size."""
+    beside = beside or {"kazedra": kazedra_config}
     peaks, peak_src = read_peaks()
     layers, vocab, B = args.layers or 4, 32768, args.batch
     if args.only in ("prefill", "decode"):
@@ -835,13 +859,14 @@ def run_arch_beside(args, arch, config_of):
                               "context": args.context or 2048, "ms_per_step": round(ms, 4)}))
             stop(eng, reqs)
         return 0
-    out = {"arch": arch, "beside": ["kazedra", "qwen3"], "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
+    out = {"arch": arch, "beside": list(beside) + ["qwen3"], "layers": layers, "vocab": vocab, "batch": B, "peaks": peak_src, "shapes": {}}
     with ClockSampler() as clocks:
         for name, (width, heads, kv, ff) in ARCH_SHAPES.items():
-            models = {arch: config_of(width, heads, kv, ff, layers, vocab),
-                      "kazedra": kazedra_config(width, heads, kv, ff, layers, vocab),
+            models = {arch: config_of(width, heads, kv, ff, layers, vocab)}
+            models.update({label: fn(width, heads, kv, ff, layers, vocab) for label, fn in beside.items()})
+            models.update({
                       "qwen3": dict(MODEL, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
-                                    intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)}
+                                    intermediate_size=ff, vocab_size=vocab, max_position_embeddings=8192)})
             row = {}
             for label, cfgd in models.items():
                 rng = random.Random(0)
@@ -861,7 +886,7 @@ def run_arch_beside(args, arch, config_of):
                               "launches_per_decode_step": (info["launches"] - before["launches"]) / args.steps,
                               "graph_replays": info["graph_replays"] - before["graph_replays"], "fallback_calls": info["fallback_calls"]}
                 del eng
-            for other in ("kazedra", "qwen3"):
+            for other in list(beside) + ["qwen3"]:
                 row["prefill_ratio_to_" + other] = round(row[arch]["prefill_2048_ms"]["median"] / row[other]["prefill_2048_ms"]["median"], 3)
                 row["decode_ratio_to_" + other] = round(row[arch]["decode_ms_per_step"] / row[other]["decode_ms_per_step"], 3)
             out["shapes"][name] = row
@@ -902,7 +927,7 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--workload", default="", choices=["", "0.6b", "14b"], help="one of the two other workloads of the baseline record")
-    ap.add_argument("--arch", default="", choices=["", "kazedra", "kuzipel", "pemidra"],
+    ap.add_argument("--arch", default="", choices=["", "kazedra", "kuzipel", "pemidra", "nizorax"],
                     help="prefill and decode of this architecture beside the Qwen3 decoder at equal sizes (not the default workload)")
     ap.add_argument("--shape", default="8b", choices=["1b", "8b"], help="with --arch and --only: which of the shapes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="with --workload: the compute type")
