@@ -722,6 +722,8 @@ constexpr int LP_PER = LP_MAX_D / 32;
 
 // Retention: proj columns [q: H*D | k: H*D | v: H*Dv | ...]; q = f(q projected), kw = f(k) * k_scale, v = f(v), scal = (q . kw, 0);
 // f the identity (act 0) or silu (act 1), in 32-bit.
+template <typename TA> __device__ __forceinline__ float lp_silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }   // 16-bit inputs: the fast forms are far below their rounding
+template <> __device__ __forceinline__ float lp_silu<float>(float x) { return silu_f(x); }
 template <typename TA>
 __global__ void __launch_bounds__(GP_BLOCK) retention_prepare_kernel(const TA* __restrict__ proj, int64_t ld, int n_tokens, int H, int D, int Dv,
                                                                      float k_scale, int act, float* __restrict__ q, float* __restrict__ kw,
@@ -737,7 +739,7 @@ __global__ void __launch_bounds__(GP_BLOCK) retention_prepare_kernel(const TA* _
     float dot = 0.f;
     for (int d = lane; d < D; d += 32) {
         float qq = to_float(row[h * D + d]), kk = to_float(row[(int64_t)H * D + h * D + d]);
-        if (act == 1) qq = silu_f(qq), kk = silu_f(kk);
+        if (act == 1) qq = lp_silu<TA>(qq), kk = lp_silu<TA>(kk);
         kk *= k_scale;
         q[(t * H + h) * D + d] = qq;
         kw[(t * H + h) * D + d] = kk;
@@ -745,7 +747,7 @@ __global__ void __launch_bounds__(GP_BLOCK) retention_prepare_kernel(const TA* _
     }
     for (int d = lane; d < Dv; d += 32) {
         const float vv = to_float(row[(int64_t)2 * H * D + h * Dv + d]);
-        v[(t * H + h) * Dv + d] = act == 1 ? silu_f(vv) : vv;
+        v[(t * H + h) * Dv + d] = act == 1 ? lp_silu<TA>(vv) : vv;
     }
     dot = warp_sum(dot);
     if (lane == 0) {

@@ -49,7 +49,7 @@ Tensor row_slice(const Tensor& t, int64_t r0, int64_t n) {
 // params: hidden_size, taps.  Tensor: weight [hidden_size, taps].
 struct ResidualConv : Mixer {
     int C, taps;
-    Tensor w;   // float32
+    Tensor w;   // float32, tap by tap: [taps, hidden_size]
     static TensorSpecs specs(const Json& p) {
         TensorSpecs s;
         s.emplace_back("weight", TensorSpec{{need_int(p, "hidden_size", "residual_conv"), need_int(p, "taps", "residual_conv")}, "vector", "normal"});
@@ -66,8 +66,11 @@ struct ResidualConv : Mixer {
     explicit ResidualConv(BuildArgs& a) {
         C = (int)need_int(a.params, "hidden_size", "residual_conv");
         taps = (int)need_int(a.params, "taps", "residual_conv");
-        w = to_float32(*a.rt, *a.store, a.tensor("weight"));
-        IMP_CUDA(cudaStreamSynchronize(a.rt->stream));
+        const std::vector<float> by_channel = download_f32(*a.rt, *a.store, a.tensor("weight"));
+        std::vector<float> by_tap((size_t)C * taps);
+        for (int c = 0; c < C; ++c)
+            for (int j = 0; j < taps; ++j) by_tap[(size_t)j * C + c] = by_channel[(size_t)c * taps + j];
+        w = upload_f32(*a.rt, *a.store, by_tap);
         a.drop("weight");
     }
     Branch forward(Step& st, Tensor x, LayerCache* cache) override {
