@@ -424,6 +424,53 @@ __global__ void __launch_bounds__(256) lsr_output_row_kernel(TA* __restrict__ y,
     }
 }
 
+// Rows whose size is a multiple of 4: four neighbouring values a thread and pass (16-byte loads of the read-out and the weight,
+// 8-byte loads of a 16-bit gate), 512 threads a token.
+template <typename TA>
+__global__ void __launch_bounds__(512) lsr_output_row_vec_kernel(TA* __restrict__ y, const float* __restrict__ o, const TA* __restrict__ gate, int64_t gate_ld,
+                                                                 const float* __restrict__ w, int act, float eps, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int64_t t = blockIdx.x;
+    const float* x = o + t * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < n; i += 512 * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    }
+    const float r = rsqrtf(block_sum(ss, scratch) / (float)n + eps);
+    const TA* gt = gate + t * gate_ld;
+    TA* dst = y + t * n;
+    for (int i = threadIdx.x * 4; i < n; i += 512 * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(x + i);
+        const float4 ww = w ? *reinterpret_cast<const float4*>(w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        float g[4], out[4];
+        if constexpr (sizeof(TA) == 4) {
+            const float4 gv = *reinterpret_cast<const float4*>(gt + i);
+            g[0] = gv.x, g[1] = gv.y, g[2] = gv.z, g[3] = gv.w;
+        } else {
+            const uint2 u = *reinterpret_cast<const uint2*>(gt + i);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+            g[0] = a.x, g[1] = a.y, g[2] = b.x, g[3] = b.y;
+        }
+        const float xs[4] = {v.x, v.y, v.z, v.w}, ws[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float a = act == 0 ? silu_f(g[k]) : 1.f / (1.f + expf(-g[k]));
+            out[k] = xs[k] * r * ws[k] * a;
+        }
+        if constexpr (sizeof(TA) == 4) {
+            *reinterpret_cast<float4*>(dst + i) = make_float4(out[0], out[1], out[2], out[3]);
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(out[0], out[1]), b = __floats2bfloat162_rn(out[2], out[3]);
+            uint2 u;
+            u.x = *reinterpret_cast<uint32_t*>(&a), u.y = *reinterpret_cast<uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(dst + i) = u;
+        }
+    }
+}
+
 // The read-out's norm and gate.  w: float32 weight or null; w_head_stride: 0 for one vector [Dv] shared by the heads, Dv for
 // a vector [H * Dv]; gate_act: 0 silu, 1 sigmoid.
 IMP_API int imp_gdr_output_ex(void* y, const float* o, const void* gate, int64_t gate_ld, const float* w, int w_head_stride, int gate_act,
@@ -449,6 +496,15 @@ IMP_API int imp_lsr_output_row(void* y, const float* o, const void* gate, int64_
     if (n_tokens == 0) return 0;
     IMP_CHECK_ARG(y && o && gate && n > 0 && gate_ld >= n && (gate_act == 0 || gate_act == 1), "imp_lsr_output_row: bad argument");
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t el = act_dtype == IMP_F32 ? 4 : 2;
+    if (n % 4 == 0 && gate_ld % 4 == 0 && (uintptr_t)o % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)gate % (4 * el) == 0 && (uintptr_t)y % (4 * el) == 0) {
+        if (act_dtype == IMP_F32)
+            imp_launch(lsr_output_row_vec_kernel<float>, dim3(n_tokens), dim3(512), 0, s, (float*)y, o, (const float*)gate, gate_ld, w, gate_act, eps, n);
+        else
+            imp_launch(lsr_output_row_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(512), 0, s, (__nv_bfloat16*)y, o, (const __nv_bfloat16*)gate, gate_ld, w,
+                       gate_act, eps, n);
+        IMP_RETURN_LAUNCH();
+    }
     if (act_dtype == IMP_F32)
         imp_launch(lsr_output_row_kernel<float>, dim3(n_tokens), dim3(256), 0, s, (float*)y, o, (const float*)gate, gate_ld, w, gate_act, eps, n);
     else
