@@ -759,16 +759,16 @@ def nizorax_config(width, heads, kv_heads, ff, layers, vocab):
     it, the same attention with routed experts (16 in 4 groups of which 2 are kept, two chosen, a shared one: together the
     dense inner size), and lightning (heads of 128 keys and 128 values: Pemidra's retention geometry) with the dense
     feed-forward; four taps on every sublayer's input."""
-    attn = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.5, "scale": 64 ** -0.5, "mask": {"size": 1024},
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 128, "diff": 0.3, "scale": 64 ** -0.5, "mask": {"size": 1024},
             "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
     n_lig = width // 128
     lig = {"heads": n_lig, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 4.0 * h / max(n_lig - 1, 1)) for h in range(n_lig)]}
     dense = {"kind": "dense", "ff": ff}
-    moe = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+    moe = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
            "shared": {"ff": ff // 3}}
     kinds = [("attention", attn, dense), ("attention", attn, moe), ("lightning", lig, dense)]
     lays = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": kinds[i % 3][2]} for i in range(layers)]
-    return {"architecture": "Nizorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+    return {"architecture": "Nizorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
             "canon": {"taps": 4}, "layers": lays, "max_positions": 8192}
 
 

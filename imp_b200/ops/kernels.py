@@ -187,6 +187,21 @@ def add_rmsnorm(h: torch.Tensor, branch, weight: torch.Tensor, out: torch.Tensor
     return out
 
 
+def add_normed_layernorm(h: Optional[torch.Tensor], branch: torch.Tensor, branch_w: torch.Tensor, branch_b: Optional[torch.Tensor],
+                         branch_eps: float, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+                         out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, write_h: bool = True) -> Optional[torch.Tensor]:
+    """h += LN(branch; branch_w, branch_b); out = LN(h; weight, bias) in one launch.  Without `h`, out = LN(branch) alone;
+    without `weight` the sum is only stored.  `rows` (int32) gathers the rows to produce and leaves h as it is."""
+    _need_cuda(h, branch, branch_w, branch_b, weight, bias, out, rows)
+    n, d = (rows.numel(), branch.shape[1]) if rows is not None else branch.shape
+    assert branch.is_contiguous() and (h is None or (h.dtype == torch.float32 and h.is_contiguous() and h.shape == branch.shape))
+    assert out is None or (out.is_contiguous() and out.dtype == branch.dtype and out.shape == (n, d))
+    L.check(L.load().imp_add_normed_layernorm(_ptr(h), branch.data_ptr(), branch_w.data_ptr(), _ptr(branch_b), float(branch_eps), _ptr(weight),
+                                              _ptr(bias), float(eps), _ptr(out), _ptr(rows), n, d, _dt(branch), _dt(branch_w),
+                                              1 if (write_h and rows is None and h is not None) else 0, _stream()), "add_normed_layernorm")
+    return out
+
+
 def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
                  weight_offset: float = 0.0) -> torch.Tensor:
     """Row-wise RMSNorm of a 2-D tensor whose rows may be strided."""

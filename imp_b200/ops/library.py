@@ -29,6 +29,8 @@ _SIGNATURES = {
     "imp_cast": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p]),
     "imp_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
                                 c_int, c_int, c_int, c_void_p]),
+    "imp_add_normed_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "imp_rmsnorm_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float,
                                  c_int, c_int, c_void_p]),
     "imp_qk_norm_rope_kv_write": (c_int, [

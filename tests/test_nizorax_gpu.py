@@ -131,6 +131,38 @@ def moe_params(d, c):
             "weight_scale": r.get("scale", 1.0), "num_groups": g.get("count", 0), "keep_groups": g.get("keep", 0)}
 
 
+# ------------------------------------------------- a branch with a norm of its own, the sum and the next norm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [70, 72, 4096, 8200, 9001])
+def test_branch_norm_sum_and_next_norm_in_one_launch(dtype, d):
+    """Widths that take each form of the kernel: rows in registers (multiples of 4 up to 8,192), rows in shared memory
+    (the rest); rows with a large mean; a gather list that leaves the stream as it is; the branch's norm alone."""
+    from imp_b200.ops import kernels as K
+    n = 7
+    bw, bb = (1 + 0.3 * rnd(d, seed=1)).to(dtype), rnd(d, seed=2).to(dtype)
+    w, b = (1 + 0.3 * rnd(d, seed=3)).to(dtype), rnd(d, seed=4).to(dtype)
+    h = rnd(n, d, seed=5) * 3 + 2.0
+    br = (rnd(n, d, seed=6) * 2 + 5.0).to(dtype)
+    normed = N.layer_norm(br.double(), bw.double(), bb.double(), 3e-5)
+    total = h.double() + normed
+    want = N.layer_norm(total, w.double(), b.double(), EPS)
+    hd, out = h.to(DEV).clone(), torch.empty(n, d, dtype=dtype, device=DEV)
+    K.add_normed_layernorm(hd, br.to(DEV), bw.to(DEV), bb.to(DEV), 3e-5, w.to(DEV), b.to(DEV), EPS, out)
+    torch.cuda.synchronize()
+    close(hd, total, torch.float32, "stream")
+    close(out, want, dtype, "normalised")
+    rows = torch.tensor([5, 0, 3], dtype=torch.int32, device=DEV)
+    hd2, out3 = h.to(DEV).clone(), torch.empty(3, d, dtype=dtype, device=DEV)
+    K.add_normed_layernorm(hd2, br.to(DEV), bw.to(DEV), bb.to(DEV), 3e-5, w.to(DEV), b.to(DEV), EPS, out3, rows=rows)
+    torch.cuda.synchronize()
+    assert torch.equal(hd2.cpu(), h), "a gather list leaves the stream as it is"
+    assert torch.equal(out3, out[rows.long()]), "the gathered rows are the rows of the whole launch"
+    alone = torch.empty(n, d, dtype=dtype, device=DEV)
+    K.add_normed_layernorm(None, br.to(DEV), bw.to(DEV), bb.to(DEV), 3e-5, None, None, 0.0, alone)
+    torch.cuda.synchronize()
+    close(alone, normed, dtype, "the branch's norm alone")
+
+
 # --------------------------------------------------------------- the convolution on a sublayer's input
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("taps, d", [(1, 40), (2, 72), (4, 300), (6, 64)])
@@ -469,6 +501,8 @@ def moe_cfg(experts, top, ff, shared, scale=1.0, groups=None):
 # shared one.  M2: no convolution, no repeated run, neither embedding nor logit scale; an attention layer without window
 # and rotation, a key head per head; experts one a token without groups; groups of one expert; a width that is no power
 # of two; pages of 4.  M3: one tap; the middle layer runs three times between the others; a layer without feed-forward.
+# M4: sizes that are multiples of nothing (a width of 70, maps of 10, values of 22, keys of 9, inner sizes 50, 12 and 10, three
+# experts): the kernels' forms for single values, the plain products, experts whose gate and up rows are not interleaved.
 MODELS = {
     "M1": ({"architecture": "Nizorax", "vocab": 97, "width": 64, "norm": {"eps": 3e-5}, "embedding": {"scale": 4.0}, "logit_scale": 0.5,
             "canon": {"taps": 3}, "loop": {"start": 0, "stop": 2, "times": 2},
@@ -486,8 +520,11 @@ MODELS = {
             "layers": [{"type": "attention", "mixer": att(2, 2, 48, 32, 40, 16), "mlp": {"kind": "dense", "ff": 64}},
                        {"type": "lightning", "mixer": lig(2, 32, 48, [0.9, 0.999]), "mlp": moe_cfg(4, 2, 32, 0, 1.5, (2, 1))},
                        {"type": "attention", "mixer": att(4, 2, 32, 32, 64, 32, base=1000.0), "mlp": None}]}, 16),
+    "M4": ({"architecture": "Nizorax", "vocab": 83, "width": 70, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0}, "canon": {"taps": 2},
+            "layers": [{"type": "attention", "mixer": att(2, 1, 10, 22, 9, 4, base=30.0), "mlp": moe_cfg(3, 2, 12, 10, 1.2)},
+                       {"type": "lightning", "mixer": lig(2, 9, 11, [0.8, 0.97]), "mlp": {"kind": "dense", "ff": 50}}]}, 8),
 }
-LENGTHS = {"M1": (1, 23, 75, 40, 130, 64), "M2": (150, 2, 33, 201, 64, 97), "M3": (70, 5, 140, 31, 64, 2)}
+LENGTHS = {"M1": (1, 23, 75, 40, 130, 64), "M2": (150, 2, 33, 201, 64, 97), "M3": (70, 5, 140, 31, 64, 2), "M4": (45, 3, 70, 20, 64, 9)}
 
 
 def make_weights(cfg, seed):
@@ -563,7 +600,7 @@ def check_rows(rows, reqs, ref, dtype, label="", unsure=()):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["M1", "M2", "M3"])
+@pytest.mark.parametrize("name", ["M1", "M2", "M3", "M4"])
 def test_replay_all_ways_of_cutting(name, dtype, nizorax_folders, tmp_path):
     folder, cfg, page, W, reqs, ref, unsure = nizorax_folders[name]
     assert len(unsure) < sum(len(v) for v in reqs.values()) // 3
@@ -591,7 +628,7 @@ def test_replay_all_ways_of_cutting(name, dtype, nizorax_folders, tmp_path):
                 assert np.array_equal(row, results[label][key]), f"{label}: {key} differs from the whole run"
 
 
-@pytest.mark.parametrize("name", ["M1", "M2", "M3"])
+@pytest.mark.parametrize("name", ["M1", "M2", "M3", "M4"])
 def test_the_stream_after_every_layer(name, nizorax_folders, tmp_path, monkeypatch):
     """The first layer run that differs names the mechanism: the stream after every layer run of one prompt, in float32."""
     folder, cfg, page, W, reqs, ref, unsure = nizorax_folders[name]
