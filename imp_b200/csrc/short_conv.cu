@@ -110,6 +110,74 @@ __global__ void __launch_bounds__(SC_BLOCK) add_conv_vec_kernel(TA* __restrict__
     }
 }
 
+// Steps of several tokens a sequence: a thread walks SC_TOK neighbouring tokens of the step for its eight channels.  The rows it
+// needs (the tokens' own and the TAPS - 1 before the first) are asked for at once and read once, the taps' weights stay in
+// registers; a token near its portion's start takes the missing inputs from its request's state.  The sum runs over the taps in
+// the order of the other forms.  TAPS at compile time, so that every row and weight has a register of its own.
+constexpr int SC_TOK = 4;
+template <typename TA, int TAPS>
+__global__ void __launch_bounds__(SC_BLOCK) add_conv_tile_kernel(TA* __restrict__ out, const TA* __restrict__ x, int64_t ld, const float* __restrict__ w,
+                                                                 const float* __restrict__ state, const int* __restrict__ seq_of_token,
+                                                                 const int* __restrict__ q_start, const int* __restrict__ slots, int n_tokens, int n_seqs,
+                                                                 int C, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int c = (blockIdx.y * SC_BLOCK + threadIdx.x) * 8;
+    if (c >= C) return;
+    const int t0 = blockIdx.x * SC_TOK;
+    F8 rows[SC_TOK + TAPS - 1];
+#pragma unroll
+    for (int i = 0; i < SC_TOK + TAPS - 1; ++i) {
+        const int r = t0 - (TAPS - 1) + i;
+        if (r >= 0 && r < n_tokens) rows[i] = load8(x + (int64_t)r * ld + c);
+    }
+    F8 wv[TAPS];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wv[j] = load8(w + (int64_t)j * C + c);
+#pragma unroll
+    for (int i = 0; i < SC_TOK; ++i) {
+        const int t = t0 + i;
+        if (t < n_tokens) {
+            const int seq = seq_of_token[t];
+            if (seq < 0 || seq >= n_seqs) {
+                if (threadIdx.x == 0 && blockIdx.y == 0) imp_report(status, IMP_BAD_SEQUENCE);
+            } else {
+                const int lt = t - q_start[seq];
+                F8 acc = rows[i + TAPS - 1];
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j) {
+                    const int s = lt - (TAPS - 1) + j;     // s >= 0: row t - (TAPS - 1) + j of the step belongs to this sequence
+                    F8 v = rows[i + j];
+                    if (s < 0) v = load8(state + ((int64_t)slots[seq] * (TAPS - 1) + (TAPS - 1 + s)) * C + c);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc.v[k] = fmaf(wv[j].v[k], v.v[k], acc.v[k]);
+                }
+                store8(out + (int64_t)t * C + c, acc);
+            }
+        }
+    }
+}
+
+template <typename TA>
+static bool launch_conv_tile(void* out, const void* x, int64_t ld, const float* w, int taps, const float* state, const int* seq_of_token, const int* q_start,
+                             const int* slots, int n_tokens, int n_seqs, int C, int* status, cudaStream_t s) {
+    const dim3 grid((unsigned)((n_tokens + SC_TOK - 1) / SC_TOK), (unsigned)((C / 8 + SC_BLOCK - 1) / SC_BLOCK));
+#define IMP_CONV_TILE(T)                                                                                                                          \
+    case T:                                                                                                                                       \
+        imp_launch(add_conv_tile_kernel<TA, T>, grid, dim3(SC_BLOCK), 0, s, (TA*)out, (const TA*)x, ld, w, state, seq_of_token, q_start, slots, \
+                   n_tokens, n_seqs, C, status);                                                                                                  \
+        return true
+    switch (taps) {
+        IMP_CONV_TILE(2);
+        IMP_CONV_TILE(3);
+        IMP_CONV_TILE(4);
+        IMP_CONV_TILE(5);
+        IMP_CONV_TILE(6);
+        default: return false;
+    }
+#undef IMP_CONV_TILE
+}
+
 template <typename TA>
 __global__ void __launch_bounds__(SC_BLOCK) polynorm_kernel(TA* __restrict__ out, const TA* __restrict__ z, int64_t ld, int n, const float* __restrict__ coef,
                                                             float eps) {
@@ -147,6 +215,12 @@ IMP_API int imp_add_conv(void* out, const void* x, int64_t ld, const float* w, i
     cudaStream_t s = (cudaStream_t)stream;
     const size_t el = dtype == IMP_F32 ? 4 : 2;
     if (C % 8 == 0 && (ld * el) % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0) {
+        if (!shift_state && n_tokens >= 64) {    // portions of prompts: the form that walks several tokens a thread
+            const bool done = dtype == IMP_F32 ? launch_conv_tile<float>(out, x, ld, w, taps, state, seq_of_token, q_start, slots, n_tokens, n_seqs, C, status, s)
+                                               : launch_conv_tile<__nv_bfloat16>(out, x, ld, w, taps, state, seq_of_token, q_start, slots, n_tokens, n_seqs, C,
+                                                                                 status, s);
+            if (done) IMP_RETURN_LAUNCH();
+        }
         const dim3 vgrid((unsigned)n_tokens, (unsigned)((C / 8 + SC_BLOCK - 1) / SC_BLOCK));
         if (dtype == IMP_F32)
             imp_launch(add_conv_vec_kernel<float>, vgrid, dim3(SC_BLOCK), 0, s, (float*)out, (const float*)x, ld, w, taps, state, seq_of_token, q_start,
