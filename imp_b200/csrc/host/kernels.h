@@ -119,6 +119,9 @@ int imp_add_layernorm_ex(float* h, float h_mult, const void* branch, const float
 int imp_add_normed_layernorm(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
                              float eps, void* out, const int* rows, int n_out_rows, int d, int act_dtype, int w_dtype, int write_h,
                              void* stream);
+int imp_add_normed_layernorm_conv(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
+                                  float eps, void* out, int n_rows, int d, int act_dtype, int w_dtype, const float* conv_w, int taps,
+                                  float* conv_state, const int* seq_of_token, const int* slots, void* stream);
 // the general scan over a decaying matrix state and the kernels around it (delta_rule.cu)
 int imp_lsr_scan(int mode, const float* kw, const float* q, const float* w, const float* p, const float* z, const float* v,
                  const float* scal, const float* head_decay, float* state, float* out, const int* q_start, const int* slots,

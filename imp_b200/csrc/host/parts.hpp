@@ -76,6 +76,16 @@ struct Tiles {
     int count = 0;
 };
 
+// What a norm may do to the rows it has just normalised, in the same kernel, when whoever arranges it asks (Step::row_op): in a
+// step of single tokens, the short convolution of the rows' reader (out = y + sum_j w[j] * input j steps back, the earlier inputs
+// in the reader's state, which the row then joins).  The norm sets `taken` if it did; otherwise the reader runs its own kernel.
+struct RowOp {
+    const float* conv_w = nullptr;   // float32 [taps, width]
+    int taps = 0, width = 0;
+    float* conv_state = nullptr;     // float32 [slots][taps - 1][width]
+    bool taken = false;
+};
+
 // ---------------------------------------------------------------------------------- one step
 struct Step {
     Runtime* rt = nullptr;
@@ -90,6 +100,7 @@ struct Step {
     Tensor embedding_out{};                    // a copy of the embedding's output, kept when a block asks for it (Block::wants_embedding)
     Tensor stream_copy{};                      // the stream in the activation type, when the block that just ran left one (post-norm
                                                // blocks: their last norm writes it beside the 32-bit stream); else null
+    RowOp* row_op = nullptr;                   // set around one add_norm call by a block that offers its reader's per-row operation
     int context = 0;                           // the sequences' mean length after this step, rounded to a power of two: what
                                                // launch choices may depend on (a decode graph is kept per batch size and context)
     int T() const { return view.n_tokens; }
@@ -174,6 +185,9 @@ struct Mixer : Part {
     // A mixer whose output ends with "+ bias" may hand that bias (float32 [hidden]) to whoever arranges it, who then adds
     // it where it combines the output anyway; from this call on the mixer leaves it out.  Null: nothing to hand over.
     virtual const float* defer_out_bias() { return nullptr; }
+    // A mixer-category part whose whole work in this step is a per-row operation on its input (see RowOp) says so here and
+    // is then not run if the norm before it took the operation.
+    virtual bool as_row_op(Step& st, LayerCache* cache, RowOp* out) { (void)st; (void)cache; (void)out; return false; }
     virtual Branch forward(Step& st, Tensor x, LayerCache* cache) = 0;
     void call(Step& st, ImpCall& c) override;
 };

@@ -89,6 +89,18 @@ struct LayerNorm : Norm {
         if (!b.empty() && (rows(b.t) != rows(h) || cols(b.t) != d || b.t.dtype != out.dtype || !contiguous(b.t)))
             fail(IMP_ERROR_INVALID_ARG, "layernorm: the branch must be dense, of the stream's shape and the output's type");
         ++rt.launches;
+        if (b.own_norm.weight && st.row_op && !rows_idx) {
+            // ... and the per-row operation of the rows' reader behind it, where the kernel's form takes it
+            RowOp& op = *st.row_op;
+            const int rc = imp_add_normed_layernorm_conv((float*)h.data, b.t.data, b.own_norm.weight, b.own_norm.bias, b.own_norm.eps, weight.data, bias.data,
+                                                         eps, out.data, (int)n, d, out.dtype, weight.dtype, op.conv_w, op.taps, op.conv_state,
+                                                         st.view.seq_of_token, st.view.state_slots, rt.stream);
+            if (rc == 0) {
+                op.taken = true;
+                return out;
+            }
+            if (rc != -2) check_launch(rc, "add_normed_layernorm_conv");   // -2: the kernel declined (width or alignment); the unfused launches follow
+        }
         if (b.own_norm.weight) {
             // the branch's own norm, the sum and this norm in one pass
             check_launch(imp_add_normed_layernorm((float*)h.data, b.t.data, b.own_norm.weight, b.own_norm.bias, b.own_norm.eps, weight.data, bias.data, eps,

@@ -73,6 +73,16 @@ struct ResidualConv : Mixer {
         w = upload_f32(*a.rt, *a.store, by_tap);
         a.drop("weight");
     }
+    // A step of single tokens: the whole part is one operation per row, which the norm before it may run in its own kernel.
+    bool as_row_op(Step& st, LayerCache* cache, RowOp* out) override {
+        if (!st.decode_only() || !cache || cache->view.kind != 2 || cache->view.n_states < 1) return false;
+        out->conv_w = (const float*)w.data;
+        out->taps = taps;
+        out->width = C;
+        out->conv_state = (float*)cache->view.states[0].data;
+        out->taken = false;
+        return true;
+    }
     Branch forward(Step& st, Tensor x, LayerCache* cache) override {
         Runtime& rt = *st.rt;
         if (!cache || cache->view.kind != 2 || cache->view.n_states < 1) fail(IMP_ERROR_INTERNAL, "residual_conv runs against a state cache");
@@ -359,20 +369,29 @@ struct SandwichBlock : Block {
         if (consumer_takes) return out;
         return Branch::of(summed(st, out));
     }
+    // What a sublayer reads: the norm of the stream (the branch added on the way), then the part in front of the sublayer.  Where
+    // that part is one operation per row in this step, the norm is offered it and the part runs only if the norm declined.
+    Tensor normed_input(Step& st, Norm* norm, Tensor h, const Branch& branch, Mixer* conv, LayerCache* c_conv) const {
+        RowOp op;
+        const bool offered = conv && conv->as_row_op(st, c_conv, &op) && cols(h) == op.width;
+        st.row_op = offered ? &op : nullptr;
+        Tensor x = norm->add_norm(st, h, branch);
+        st.row_op = nullptr;
+        if (conv && !(offered && op.taken)) x = summed(st, conv->forward(st, x, c_conv));
+        return x;
+    }
     Branch forward(Step& st, Tensor h, const Branch& pending, LayerCache* cache) override {
         // caches in slot order: (conv1,) mixer, (conv2); a block whose only mixer has no cache gets a null pointer
         LayerCache* c_conv1 = conv1 ? &cache[0] : nullptr;
         LayerCache* c_mixer = conv1 ? &cache[1] : cache;
         LayerCache* c_conv2 = conv2 ? &cache[2] : nullptr;
         if (c_mixer && !c_mixer->view.kind) c_mixer = nullptr;
-        Tensor x = norm1->add_norm(st, h, pending);
-        if (conv1) x = summed(st, conv1->forward(st, x, c_conv1));
+        Tensor x = normed_input(st, norm1, h, pending, conv1, c_conv1);
         mixer_->defer_out = false;
         Branch a = with_norm(st, mixer_->forward(st, x, c_mixer), own1, ffn ? norm2->takes_normed_branch() : norm_pending);
         stage(st, "mixer", a);
         if (!ffn) return a;
-        x = norm2->add_norm(st, h, a);
-        if (conv2) x = summed(st, conv2->forward(st, x, c_conv2));
+        x = normed_input(st, norm2, h, a, conv2, c_conv2);
         ffn->defer_out = false;
         Branch f = with_norm(st, ffn->forward(st, x), own2, norm_pending);
         stage(st, "feed_forward", f);

@@ -336,13 +336,21 @@ __global__ void __launch_bounds__(LN_BLOCK) add_normed_layernorm_kernel(float* _
         orow[i] = from_float<TA>(fmaf((hs[i] - mean) * inv, to_float(w[i]), bias ? to_float(bias[i]) : 0.f));
 }
 
+template <typename T> __device__ __forceinline__ float4 round_as(float4 v) { return v; }
+template <> __device__ __forceinline__ float4 round_as<__nv_bfloat16>(float4 v) {
+    const float2 a = __bfloat1622float2(__floats2bfloat162_rn(v.x, v.y)), b = __bfloat1622float2(__floats2bfloat162_rn(v.z, v.w));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // The same for rows whose width is a multiple of 4, up to 256 x NV x 4 columns: the branch row and the stream's row are read
 // once with 16-byte loads and stay in registers between the passes.
 template <typename TA, typename TW, int NV>
 __global__ void __launch_bounds__(LN_BLOCK) add_normed_layernorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ branch, const TW* __restrict__ bw,
                                                                             const TW* __restrict__ bb, float eps_b, const TW* __restrict__ w,
                                                                             const TW* __restrict__ bias, float eps, TA* __restrict__ out,
-                                                                            const int* __restrict__ rows, int d, int write_h) {
+                                                                            const int* __restrict__ rows, int d, int write_h,
+                                                                            const float* __restrict__ conv_w, int taps, float* __restrict__ conv_state,
+                                                                            const int* __restrict__ seq_of_token, const int* __restrict__ slots) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ float scratch[33];
@@ -402,27 +410,48 @@ __global__ void __launch_bounds__(LN_BLOCK) add_normed_layernorm_vec_kernel(floa
         if (i < d) {
             const float4 ww = Vec4<TW>::load(w + i);
             const float4 bv = bias ? Vec4<TW>::load(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            Vec4<TA>::store(orow + i, make_float4(fmaf((v[e].x - mean) * inv, ww.x, bv.x), fmaf((v[e].y - mean) * inv, ww.y, bv.y),
-                                                  fmaf((v[e].z - mean) * inv, ww.z, bv.z), fmaf((v[e].w - mean) * inv, ww.w, bv.w)));
+            float4 y = make_float4(fmaf((v[e].x - mean) * inv, ww.x, bv.x), fmaf((v[e].y - mean) * inv, ww.y, bv.y),
+                                   fmaf((v[e].z - mean) * inv, ww.z, bv.z), fmaf((v[e].w - mean) * inv, ww.w, bv.w));
+            if (conv_w) {
+                // A step of single tokens: the short convolution that the reader of this row would run next (y + sum_j w[j] * input j
+                // steps back, the inputs before this token in the request's state), and the state's shift.  The row is rounded to the
+                // activation type first, as the kernel that reads stored rows sees it, and the sum runs in that kernel's order.
+                y = round_as<TA>(y);
+                float* st = conv_state + (int64_t)slots[seq_of_token[r]] * (taps - 1) * d + i;
+                float4 acc = y;
+                for (int j = 0; j + 1 < taps; ++j) {
+                    const float4 cw = Vec4<float>::load(conv_w + (int64_t)j * d + i), sv = Vec4<float>::load(st + (int64_t)j * d);
+                    acc.x = fmaf(cw.x, sv.x, acc.x), acc.y = fmaf(cw.y, sv.y, acc.y), acc.z = fmaf(cw.z, sv.z, acc.z), acc.w = fmaf(cw.w, sv.w, acc.w);
+                    if (j > 0) Vec4<float>::store(st + (int64_t)(j - 1) * d, sv);      // this thread alone reads and writes these entries
+                }
+                const float4 cw = Vec4<float>::load(conv_w + (int64_t)(taps - 1) * d + i);
+                acc.x = fmaf(cw.x, y.x, acc.x), acc.y = fmaf(cw.y, y.y, acc.y), acc.z = fmaf(cw.z, y.z, acc.z), acc.w = fmaf(cw.w, y.w, acc.w);
+                if (taps > 1) Vec4<float>::store(st + (int64_t)(taps - 2) * d, y);
+                y = acc;
+            }
+            Vec4<TA>::store(orow + i, y);
         }
     }
 }
 
 template <typename TA, typename TW>
 static cudaError_t launch_normed_layernorm(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
-                                           float eps, void* out, const int* rows, int n, int d, int write_h, cudaStream_t s) {
+                                           float eps, void* out, const int* rows, int n, int d, int write_h, cudaStream_t s,
+                                           const float* conv_w = nullptr, int taps = 0, float* conv_state = nullptr, const int* seq_of_token = nullptr,
+                                           const int* slots = nullptr) {
     const auto al = [](const void* p, size_t n) { return (uintptr_t)p % n == 0; };
     if (h && d % 4 == 0 && d <= LN_BLOCK * 4 * 8 && al(h, 16) && al(branch, 8) && al(out, 8) && al(bw, 16) && al(bb, 16) && al(w, 16) && al(bias, 16)) {
         const int nv = (d / 4 + LN_BLOCK - 1) / LN_BLOCK;
 #define IMP_NLN(NV)                                                                                                                                     \
     imp_launch(add_normed_layernorm_vec_kernel<TA, TW, NV>, dim3(n), dim3(LN_BLOCK), 0, s, h, (const TA*)branch, (const TW*)bw, (const TW*)bb, eps_b, \
-               (const TW*)w, (const TW*)bias, eps, (TA*)out, rows, d, write_h)
+               (const TW*)w, (const TW*)bias, eps, (TA*)out, rows, d, write_h, conv_w, taps, conv_state, seq_of_token, slots)
         if (nv <= 1) return IMP_NLN(1);
         if (nv <= 2) return IMP_NLN(2);
         if (nv <= 4) return IMP_NLN(4);
         return IMP_NLN(8);
 #undef IMP_NLN
     }
+    if (conv_w) return cudaErrorNotSupported;     // only the form with rows in registers runs the convolution
     const size_t smem = (size_t)2 * d * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(add_normed_layernorm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -452,6 +481,36 @@ IMP_API int imp_add_normed_layernorm(float* h, const void* branch, const void* b
                                : launch_normed_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, bw, bb, eps_b, w, bias, eps, out, rows, n_out_rows, d, write_h, s);
     if (e != cudaSuccess) {
         imp_set_error("imp_add_normed_layernorm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// imp_add_normed_layernorm for a step of single tokens (row r is sequence seq_of_token[r]'s only token) with the short
+// convolution of the row's reader behind the second norm: out = y + sum_j conv_w[j] * (input j steps back), conv_w float32
+// [taps, d], the earlier inputs in conv_state [slot][taps - 1][d] (float32), which is shifted by this row.  Returns
+// IMP_ERR_UNSUPPORTED, having launched nothing, for widths and alignments that the form with rows in registers does not take.
+IMP_API int imp_add_normed_layernorm_conv(float* h, const void* branch, const void* bw, const void* bb, float eps_b, const void* w, const void* bias,
+                                          float eps, void* out, int n_rows, int d, int act_dtype, int w_dtype, const float* conv_w, int taps,
+                                          float* conv_state, const int* seq_of_token, const int* slots, void* stream) {
+    if (n_rows == 0) return 0;
+    IMP_CHECK_ARG(h && branch && bw && w && out && d > 0 && conv_w && taps >= 1 && (taps == 1 || conv_state) && seq_of_token && slots,
+                  "imp_add_normed_layernorm_conv: bad argument");
+    // Up to 2,048 columns (two vectors a thread): there the saved launch wins (8 sequences at width 1024: 0.344 -> 0.329 ms a decode step of
+    // four layers); at width 4096 the one CTA a token that also walks the state and the taps' weights lost (0.682 -> 0.713 ms) to the
+    // separate kernel, which spreads a token over more CTAs.
+    if ((uintptr_t)conv_w % 16 || (uintptr_t)conv_state % 16 || d % 4 || d > LN_BLOCK * 4 * 2) return IMP_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (act_dtype == IMP_F32)
+        e = w_dtype == IMP_F32 ? launch_normed_layernorm<float, float>(h, branch, bw, bb, eps_b, w, bias, eps, out, nullptr, n_rows, d, 1, s, conv_w, taps, conv_state, seq_of_token, slots)
+                               : launch_normed_layernorm<float, __nv_bfloat16>(h, branch, bw, bb, eps_b, w, bias, eps, out, nullptr, n_rows, d, 1, s, conv_w, taps, conv_state, seq_of_token, slots);
+    else
+        e = w_dtype == IMP_F32 ? launch_normed_layernorm<__nv_bfloat16, float>(h, branch, bw, bb, eps_b, w, bias, eps, out, nullptr, n_rows, d, 1, s, conv_w, taps, conv_state, seq_of_token, slots)
+                               : launch_normed_layernorm<__nv_bfloat16, __nv_bfloat16>(h, branch, bw, bb, eps_b, w, bias, eps, out, nullptr, n_rows, d, 1, s, conv_w, taps, conv_state, seq_of_token, slots);
+    if (e == cudaErrorNotSupported) return IMP_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) {
+        imp_set_error("imp_add_normed_layernorm_conv: %s", cudaGetErrorString(e));
         return (int)e;
     }
     return 0;
